@@ -13,7 +13,7 @@ Lower down: `engine.step(entries, want)` is the one step function (logits at wan
 
 from . import models as _models  # registers the architectures  # noqa: F401
 from . import parts as _parts  # registers the built-in parts  # noqa: F401
-from .config import Qwen3Config, read_config_json
+from .config import KebisunConfig, Qwen3Config, read_config_json
 from .engine.backends import BACKENDS, available_backends_help, resolve_backend
 from .engine.engine import Engine
 from .engine.generate import (GenerationOptions, GenerationResult, GenerationStats,
@@ -31,7 +31,7 @@ __version__ = "0.1.0"
 
 __all__ = [
     "Engine", "generate", "GenerationOptions", "GenerationResult", "GenerationStats", "SamplingParams",
-    "Qwen3Config", "read_config_json", "Runtime", "DecoderModel", "load_model", "random_model", "write_random_model",
+    "Qwen3Config", "KebisunConfig", "read_config_json", "Runtime", "DecoderModel", "load_model", "random_model", "write_random_model",
     "register_architecture", "register_part", "build_part", "config_from_json", "architectures",
     "BACKENDS", "available_backends_help", "resolve_backend", "detect_repetition_loop",
     "HerbertError", "ConfigError", "WeightError", "SafeTensorsError", "CacheError", "BackendError",

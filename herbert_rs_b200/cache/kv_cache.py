@@ -3,9 +3,10 @@
 What a mixer needs is declared as a `CacheNeed`; schedule steps with equal needs share a
 group, and every group has storage of its own:
 
-* key/value groups: one tensor [entries, 2, pages, kv_heads, page_size, head_dim]; a sequence
-  holds a list of pages per group (logical page i = positions i*page_size ...).  A group with a
-  window gives pages back as soon as no future query can reach them.
+* key/value groups: one tensor [entries, planes, pages, kv_heads, page_size, head_dim] (two planes:
+  keys and values; one plane for a mixer that keeps a single vector per token from which both
+  follow); a sequence holds a list of pages per group (logical page i = positions i*page_size ...).
+  A group with a window gives pages back as soon as no future query can reach them.
 * state groups: one tensor [entries, slots, *shape], zeroed when a slot is handed out.
 
 A slot stands for one sequence of a batch: its length, its pages, its state rows.  Slots and
@@ -35,6 +36,7 @@ class KVNeed:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None  # None: all keys stay; n: only the last n are ever read
+    planes: int = 2               # 2: keys and values; 1: one stored vector per token and head
 
 
 @dataclass(frozen=True)
@@ -55,7 +57,7 @@ class CacheView:
 
     kv_group: Optional[int] = None      # index into StepBatch.pages
     k: Optional[torch.Tensor] = None    # [pages, kv_heads, page_size, head_dim]
-    v: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None    # None in a group of one plane
     writes_kv: bool = True              # False: this step reads what another step stored
     state: Optional[torch.Tensor] = None  # [slots, *shape]
     page_size: int = 0
@@ -91,7 +93,8 @@ class SequenceCache:
                 if not (0 <= src < i) or reads_cache_of[src] is not None:
                     raise CacheError(f"schedule step {i} reads the cache of step {src}, which must be an earlier step that stores")
                 if needs[src].kv is None or need.kv is None or \
-                        (needs[src].kv.num_kv_heads, needs[src].kv.head_dim) != (need.kv.num_kv_heads, need.kv.head_dim):
+                        (needs[src].kv.num_kv_heads, needs[src].kv.head_dim, needs[src].kv.planes) != \
+                        (need.kv.num_kv_heads, need.kv.head_dim, need.kv.planes):
                     raise CacheError(f"schedule step {i} cannot read the cache of step {src}: key/value shapes differ")
                 g, e, _ = self.step_kv[src]
                 self.step_kv.append((g, e, False))
@@ -125,7 +128,7 @@ class SequenceCache:
         if device is not None:
             for g, need in enumerate(self.kv_needs):
                 self.kv.append(torch.zeros(
-                    (len(self._kv_entries[g]), 2, num_pages, need.num_kv_heads, page_size, need.head_dim),
+                    (len(self._kv_entries[g]), need.planes, num_pages, need.num_kv_heads, page_size, need.head_dim),
                     dtype=dtype, device=device))
             for g, need in enumerate(self.state_needs):
                 self.state.append(torch.zeros((len(self._state_entries[g]), num_slots, *need.shape),
@@ -138,7 +141,7 @@ class SequenceCache:
 
     def bytes_per_token(self) -> int:
         es = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(e) * n.num_kv_heads * n.head_dim * es for n, e in zip(self.kv_needs, self._kv_entries))
+        return sum(n.planes * len(e) * n.num_kv_heads * n.head_dim * es for n, e in zip(self.kv_needs, self._kv_entries))
 
     # -- slots -----------------------------------------------------------------------------
     def alloc_slot(self) -> int:
@@ -263,7 +266,8 @@ class SequenceCache:
             g, e, writes = kv
             v.kv_group, v.writes_kv = g, writes
             if self.kv:
-                v.k, v.v = self.kv[g][e, 0], self.kv[g][e, 1]
+                v.k = self.kv[g][e, 0]
+                v.v = self.kv[g][e, 1] if self.kv_needs[g].planes > 1 else None
         st = self.step_state[step]
         if st is not None and self.state:
             g, e = st

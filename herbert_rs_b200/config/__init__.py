@@ -2,10 +2,12 @@
 
 from .base import Reader, read_config_json
 from .qwen3 import Qwen3Config
-from .specs import (AttentionSpec, BlockSpec, ModelSpec, NormSpec, PositionSpec,
-                    ScheduleStep, SwiGLUSpec, identity_schedule)
+from .kebisun import KebisunConfig
+from .specs import (AttentionSpec, BlockSpec, GatedLinearAttentionSpec, LatentAttentionSpec, ModelSpec, NormSpec,
+                    PositionSpec, RoutedFFSpec, ScaledRotarySpec, ScheduleStep, SwiGLUSpec, identity_schedule)
 
 __all__ = [
-    "Reader", "read_config_json", "Qwen3Config", "AttentionSpec", "BlockSpec", "ModelSpec",
+    "Reader", "read_config_json", "Qwen3Config", "KebisunConfig", "AttentionSpec", "GatedLinearAttentionSpec",
+    "LatentAttentionSpec", "RoutedFFSpec", "ScaledRotarySpec", "BlockSpec", "ModelSpec",
     "NormSpec", "PositionSpec", "ScheduleStep", "SwiGLUSpec", "identity_schedule",
 ]

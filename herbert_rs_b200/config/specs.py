@@ -19,11 +19,13 @@ from typing import Optional, Sequence
 
 @dataclass(frozen=True)
 class NormSpec:
-    """A normalisation over the last axis.  kind "rmsnorm": y = x / sqrt(mean(x^2) + eps) * w."""
+    """A normalisation over the last axis.  kind "rmsnorm": y = x / sqrt(mean(x^2) + eps) * w;
+    kind "layernorm": y = (x - mean(x)) / sqrt(var(x) + eps) * w (no bias)."""
 
     dim: int
     eps: float
     kind: str = "rmsnorm"
+    weight_name: str = "weight"     # the weight's tensor name under the part's prefix
 
 
 @dataclass(frozen=True)
@@ -35,6 +37,64 @@ class PositionSpec:
     theta: float
     max_position: int
     kind: str = "rope"
+
+
+@dataclass(frozen=True)
+class ScaledRotarySpec:
+    """Half-split rotary pairs whose angles are computed from the position (no table, no longest
+    position), optionally with frequencies stretched band by band.  f_i = theta^(-2i/rotary_dim);
+    with `factor` set: d(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta),
+    lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), rotary_dim - 1),
+    r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), f_i <- f_i / factor * r_i + f_i * (1 - r_i),
+    and cos and sin are both multiplied by 0.1 ln(factor) + 1."""
+
+    rotary_dim: int
+    theta: float
+    factor: Optional[float] = None
+    original: float = 0.0
+    fast: float = 0.0
+    slow: float = 0.0
+    kind: str = "scaled_rope"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Softmax attention whose keys and values are products of one cached latent per token.
+    Per head: `nope_dim` unrotated and `rope_dim` rotated query/key channels, values of `v_dim`;
+    queries through a latent of `q_rank` (None: straight from the input), keys and values from one
+    of `kv_rank`, plus one rotated key part shared by all heads.  `sink`: a learned number per head
+    joins the softmax's denominator.  `gate`: the heads' outputs are multiplied by sigmoid(G h)."""
+
+    hidden_size: int
+    num_heads: int
+    nope_dim: int
+    rope_dim: int
+    v_dim: int
+    kv_rank: int
+    scale: float
+    norm_eps: float
+    q_rank: Optional[int] = None
+    position: Optional[ScaledRotarySpec] = None
+    window: Optional[int] = None
+    sink: bool = False
+    gate: bool = False
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec:
+    """Linear attention with a state matrix per head and a decay per key channel:
+    S_t = diag(a_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t, a = sigmoid(W2 W1 h + b)^(1/tau);
+    per-head RMSNorm of o, gate silu(G h), output product."""
+
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    decay_rank: int
+    decay_tau: float
+    norm_eps: float
+    kind: str = "gla"
 
 
 @dataclass(frozen=True)
@@ -54,11 +114,32 @@ class AttentionSpec:
 
 @dataclass(frozen=True)
 class SwiGLUSpec:
-    """Dense gated feed-forward: down(silu(gate(x)) * up(x))."""
+    """Dense gated feed-forward: down(act(gate(x)) * up(x)); act "silu", "gelu_tanh" or "gelu".
+    `names`: the tensors of gate, up and down."""
 
     hidden_size: int
     intermediate_size: int
     kind: str = "swiglu"
+    activation: str = "silu"
+    names: tuple = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+
+
+@dataclass(frozen=True)
+class RoutedFFSpec:
+    """A mixture of small feed-forwards down(act(up(x))) without biases: a token uses the `top_k`
+    experts with the largest softmax(router x) (taken over all experts), weighted by those values,
+    divided by their sum only with `renormalize`.  Tensor names: `router_name`, and
+    `expert_names` formatted with the expert's index for up and down."""
+
+    hidden_size: int
+    num_experts: int
+    top_k: int
+    expert_size: int
+    activation: str = "gelu"
+    renormalize: bool = False
+    router_name: str = "router"
+    expert_names: tuple = ("e{e}.up", "e{e}.down")
+    kind: str = "moe"
 
 
 @dataclass(frozen=True)
@@ -66,6 +147,9 @@ class BlockSpec:
     """One layer: how a mixer, a feed-forward and their norms are arranged.
 
     kind "prenorm": h = x + mixer(norm1(x)); out = h + ffn(norm2(h)).
+    kind "sublayer_norm": h = x + s1 * norm1(mixer(x)); out = h + s2 * norm2(ffn(h)): the sublayers
+    read the stream itself and their results are normed; s1, s2 are per-channel scales named by
+    `layer_scale` (None: no scales); `ffn` may be None (then the layer ends after the mixer).
     `names` maps the block's local part names to the sub-prefixes used in tensor names.
     """
 
@@ -74,6 +158,7 @@ class BlockSpec:
     norm1: NormSpec
     norm2: NormSpec
     kind: str = "prenorm"
+    layer_scale: Optional[tuple] = None
     names: tuple = (
         ("norm1", "input_layernorm"),
         ("mixer", "self_attn"),
@@ -117,6 +202,7 @@ class ModelSpec:
     # rows per token, which the caller may give per sequence (Engine.step(..., positions=...)) and
     # which default to the token's index in its sequence in every component.
     position_components: int = 1
+    embedding_scale: float = 1.0                  # the embedding rows are multiplied by this
     extra: dict = field(default_factory=dict)     # free for an architecture's own model class
 
 

@@ -18,6 +18,11 @@ extern "C" {
 #define HB_EPI_RESIDUAL 2   // C (float)           += A W^T
 #define HB_EPI_SWIGLU 3     // C (activation dtype) = silu(gate) * up, W rows in groups of 8 gate, 8 up
 
+// activations of the gated and routed feed-forwards
+#define HB_ACT_SILU 0       // z / (1 + exp(-z))
+#define HB_ACT_GELU_TANH 1  // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+#define HB_ACT_GELU 2       // 0.5 z (1 + erf(z / sqrt(2)))
+
 
 // attention_decode.cu: decode attention over the paged cache (one query per sequence, keys cut into splits)
 long long hb_attention_decode_scratch_floats(int n_seqs, int nh, int hd, int nsplit);
@@ -47,11 +52,11 @@ int hb_attention_simt(int dtype, const void* q, int ldq, void* out, int ldo, con
 
 // elementwise.cu: embedding, RMSNorm, SwiGLU, head norm + rotation + cache write, residual sum, shared-norm finish
 int hb_embed(int dtype, const void* table, const int* ids, float* out, int n_tokens, int hidden, int vocab,
-    void* stream);
+    float scale, void* stream);
 int hb_rmsnorm(int dtype, const float* x, const float* w, void* out, const int* rows, int n_rows, int dim,
     float eps, void* stream);
 int hb_swiglu(int dtype, const void* gu, int ld, void* out, int ldo, int n_tokens, int inter, int interleave,
-    void* stream);
+    int act, void* stream);
 int hb_qk_norm_rope_cache(int dtype, void* qkv, int ld, const float* qw, const float* kw, float eps, const
     float* cos_tab, const float* sin_tab, int rot, int table_rows, const int* tok_seq, const int* tok_pos,
     const int* seq_pages, int pages_stride, void* kcache, void* vcache, int n_tokens, int nh, int nkv, int hd,
@@ -108,6 +113,42 @@ int hb_gemm_tcgen05_norm_parts(int M, int N);
 int hb_gemm_tcgen05_norm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N,
     int K, int epi, const float* in_sumsq, int in_parts, int in_stride, float in_eps, const float* out_w,
     void* out_xw, int out_ld, float* out_sumsq, int out_stride, int* error_flag, void* stream);
+
+// gla.cu: gated linear attention: decays, the recurrence over a step's tokens, output norm and gate
+int hb_gla_decay(int dtype, const float* low, int ld, const void* w2, const float* bias, float inv_tau, float* a,
+    int n_tokens, int channels, int low_rank, void* stream);
+int hb_gla_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay, float* state,
+    const int* seq_slot, const int* seq_start, float* out, int ldo, int n_seqs, int heads, int dk, int dv, float
+    qscale, void* stream);
+int hb_gla_output(int dtype, const float* o, int ldo, const float* w, float eps, const float* gate, int ldg,
+    void* y, int ldy, int n_tokens, int heads, int dv, void* stream);
+
+// latent_attention.cu: attention over a cached latent (one shared key/value vector per token), with a sink
+int hb_latent_kv_store(int dtype, const float* kv, int ld, const float* norm_w, float eps, const float* freq,
+    float mscale, int rank, int rot, const int* tok_seq, const int* tok_pos, const int* seq_pages, int
+    pages_stride, void* cache, int n_tokens, int page_size, void* stream);
+int hb_rotate_heads(const float* in, int ld_in, int in_head_stride, int in_offset, float* out, int ld_out, int
+    out_head_stride, int out_offset, const float* freq, float mscale, const int* tok_pos, int n_tokens, int
+    heads, int rot, float scale, void* stream);
+int hb_headwise_gemm(int dtype, int out_dtype, const float* in, int ld_in, int in_head_stride, const void* w,
+    void* out, int ld_out, int out_head_stride, const float* gate, int ld_gate, int n_tokens, int heads, int K,
+    int N, float scale, void* stream);
+int hb_latent_attention(int dtype, const float* q, int ldq, float* out, int ldo, const void* cache, const float*
+    sink, const int* tok_seq, const int* tok_pos, const int* seq_pages, int pages_stride, int n_tokens, int
+    heads, int rank, int rot, int page_size, int window, void* stream);
+
+// layernorm.cu: layer normalisation (weight, no bias), alone and with the scaled residual sum after it
+int hb_layernorm(int dtype, const float* x, const float* w, void* out, const int* rows, int n_rows, int dim,
+    float eps, void* stream);
+int hb_layernorm_residual(int dtype, const float* y, int ldy, const float* w, const float* scale, float* x, void*
+    h, int n_rows, int dim, float eps, void* stream);
+
+// moe.cu: routed feed-forward: router with softmax and choice, the chosen experts' two products
+int hb_moe_route(int dtype, const void* h, int ld, const void* w_router, int* ids, float* weights, int
+    n_tokens, int D, int E, int top, int renorm, void* stream);
+int hb_moe_experts(int dtype, const void* h, int ld, const void* up, const void* down, const int* ids, const
+    float* weights, void* mid, float* y, int ldy, int n_tokens, int D, int F, int top, int act, int accumulate,
+    void* stream);
 
 // sampling.cu: argmax and temperature / top-k / top-p sampling
 int hb_argmax(const float* logits, int ld, int n_rows, int vocab, int* out, void* scratch, long long

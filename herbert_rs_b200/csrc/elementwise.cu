@@ -1,7 +1,7 @@
 // Embedding gather, RMSNorm, SwiGLU and the fused per-head norm + rotation + cache write.
 //
 // Formulas (reference, CPU path):
-//   embedding   x[t,:] = float(E[id_t,:])                      generic_model.rs:104-111
+//   embedding   x[t,:] = float(E[id_t,:]) * scale (1 there)    generic_model.rs:104-111
 //   RMSNorm     r = 1/sqrt(sum(x^2)/dim + eps); y = (x*r)*w    kernels.rs:54-64
 //   SwiGLU      silu(g) = g/(1+exp(-g)); a = silu(g)*u         kernels.rs:677-687
 //   head norm   RMSNorm over head_dim, one weight for all heads generic_attention/mod.rs:62-76
@@ -15,7 +15,7 @@
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int hidden, int vocab) {
+                             float* __restrict__ out, int hidden, int vocab, float scale) {
   pdl_wait();
   pdl_launch();
   const int t = blockIdx.x;
@@ -26,23 +26,23 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     return;
   }
   const T* row = table + (size_t)id * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
 }
 
 template <typename T>
 static int embed_launch(const void* table, const int* ids, float* out, int n_tokens, int hidden,
-                        int vocab, void* stream) {
+                        int vocab, float scale, void* stream) {
   HB_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: sizes must be positive");
   int threads = hidden >= 1024 ? 256 : 128;
-  hb_launch(embed_kernel<T>, dim3(n_tokens), dim3(threads), 0, (cudaStream_t)stream, (const T*)table, ids, out, hidden, vocab);
+  hb_launch(embed_kernel<T>, dim3(n_tokens), dim3(threads), 0, (cudaStream_t)stream, (const T*)table, ids, out, hidden, vocab, scale);
   HB_CHECK_LAUNCH("embed");
   return 0;
 }
 
 extern "C" int hb_embed(int dtype, const void* table, const int* ids, float* out, int n_tokens,
-                        int hidden, int vocab, void* stream) {
-  return dtype == HB_F32 ? embed_launch<float>(table, ids, out, n_tokens, hidden, vocab, stream)
-                         : embed_launch<bf16>(table, ids, out, n_tokens, hidden, vocab, stream);
+                        int hidden, int vocab, float scale, void* stream) {
+  return dtype == HB_F32 ? embed_launch<float>(table, ids, out, n_tokens, hidden, vocab, scale, stream)
+                         : embed_launch<bf16>(table, ids, out, n_tokens, hidden, vocab, scale, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -132,9 +132,10 @@ extern "C" int hb_rmsnorm(int dtype, const float* x, const float* w, void* out, 
 // ---------------------------------------------------------------------------------------------
 // gu: [n_tokens, 2*inter] with leading dimension ld.  interleave == 0: gate columns [0, inter),
 // up columns [inter, 2*inter).  interleave == 8: blocks of 16 columns, 8 gate then 8 up.
+// out = act(gate) * up; act: silu, or gelu in its tanh or erf form (HB_ACT_*).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int ldo,
-                              int inter, int interleave) {
+                              int inter, int interleave, int act) {
   pdl_wait();
   pdl_launch();
   const int t = blockIdx.y;
@@ -150,21 +151,23 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ 
     ui = gi + interleave;
   }
   const float g = to_f32(row[gi]), u = to_f32(row[ui]);
-  const float a = (g / (1.0f + expf(-g))) * u;
+  const float a = (act == HB_ACT_GELU_TANH ? 0.5f * g * (1.0f + tanhf(0.79788456080286535588f * (g + 0.044715f * g * g * g)))
+                   : act == HB_ACT_GELU    ? 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f))
+                                           : g / (1.0f + expf(-g))) * u;
   out[(size_t)t * ldo + i] = from_f32<T>(a);
 }
 
 extern "C" int hb_swiglu(int dtype, const void* gu, int ld, void* out, int ldo, int n_tokens,
-                         int inter, int interleave, void* stream) {
+                         int inter, int interleave, int act, void* stream) {
   HB_REQUIRE(n_tokens > 0 && inter > 0, "swiglu: sizes must be positive");
   HB_REQUIRE(interleave == 0 || (interleave > 0 && inter % interleave == 0),
              "swiglu: intermediate size %d is no multiple of the interleave %d", inter, interleave);
   HB_REQUIRE(n_tokens <= 65535, "swiglu: at most 65535 tokens per call, got %d", n_tokens);
   dim3 grid(ceil_div(inter, 256), n_tokens);
   if (dtype == HB_F32)
-    hb_launch(swiglu_kernel<float>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const float*)gu, ld, (float*)out, ldo, inter, interleave);
+    hb_launch(swiglu_kernel<float>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const float*)gu, ld, (float*)out, ldo, inter, interleave, act);
   else
-    hb_launch(swiglu_kernel<bf16>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const bf16*)gu, ld, (bf16*)out, ldo, inter, interleave);
+    hb_launch(swiglu_kernel<bf16>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const bf16*)gu, ld, (bf16*)out, ldo, inter, interleave, act);
   HB_CHECK_LAUNCH("swiglu");
   return 0;
 }

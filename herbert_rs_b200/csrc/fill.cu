@@ -127,9 +127,12 @@ __device__ __forceinline__ float cast_in(const bf16* p, long long i) { return __
 __device__ __forceinline__ float cast_in(const __half* p, long long i) { return __half2float(p[i]); }
 
 // round_bf16: the value passes through bfloat16 (round to nearest even) whatever the output type,
-// which is what the reference does to every F32 tensor it loads.
+// which is what the reference does to every F32 tensor it loads.  Also used inside a step (the
+// residual stream as a sublayer's input), so it waits for the kernel before it like every step kernel.
 template <typename S, typename D>
 __global__ void cast_kernel(const S* __restrict__ in, D* __restrict__ out, long long n, int round_bf16) {
+  pdl_wait();
+  pdl_launch();
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
     float v = cast_in(in, i);

@@ -1,0 +1,161 @@
+// Gated linear attention: a matrix of state per head that decays channel by channel.
+//
+//   a_t = sigmoid(z_t)^(1/tau),  z_t = W2 (W1 h_t) + b      one decay per key channel, in (0, 1)
+//   S_t = diag(a_t) S_{t-1} + k_t v_t^T                      S: [key channels][value channels], float
+//   o_t = S_t^T q_t                                          q already scaled
+//   y_t = RMSNorm(o_t) * w * silu(g_t)                       per head, one weight vector for all heads
+//
+// The state of a sequence lives in its slot of the cache's state region ([slots][heads][dk][dv]
+// floats, zero when the slot is handed out) and is carried from step to step: a step reads it,
+// runs its tokens in order and writes it back, so a prompt cut into pieces, or decoded token by
+// token, gives the state the whole prompt gives.  Decays, their logarithms, the state and the
+// norm are float on both paths; q, k, v, g and W1 h come from the projection as floats.
+#include "api.h"
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// a[t, c] = exp(logsigmoid(z) / tau),  z = b[c] + sum_r low[t, r] * W2[c, r].  One thread per (t, c).
+template <typename T>
+__global__ void gla_decay_kernel(const float* __restrict__ low, int ld, const T* __restrict__ w2, const float* __restrict__ bias,
+                                 float inv_tau, float* __restrict__ a, int n_tokens, int C, int R) {
+  pdl_wait();
+  pdl_launch();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n_tokens * C) return;
+  const int t = (int)(idx / C), c = (int)(idx % C);
+  const float* lr = low + (size_t)t * ld;
+  const T* wr = w2 + (size_t)c * R;
+  float z = bias ? bias[c] : 0.0f;
+  for (int r = 0; r < R; ++r) z = fmaf(lr[r], to_f32(wr[r]), z);
+  const float ls = fminf(z, 0.0f) - log1pf(expf(-fabsf(z)));  // log sigmoid(z)
+  a[idx] = expf(ls * inv_tau);
+}
+
+extern "C" int hb_gla_decay(int dtype, const float* low, int ld, const void* w2, const float* bias, float inv_tau, float* a,
+                            int n_tokens, int channels, int low_rank, void* stream) {
+  HB_REQUIRE(n_tokens > 0 && channels > 0 && low_rank > 0, "gla_decay: sizes must be positive");
+  const long long n = (long long)n_tokens * channels;
+  dim3 grid((unsigned)ceil_div_ll(n, 256));
+  if (dtype == HB_F32)
+    hb_launch(gla_decay_kernel<float>, grid, dim3(256), 0, (cudaStream_t)stream, low, ld, (const float*)w2, bias, inv_tau, a, n_tokens, channels, low_rank);
+  else
+    hb_launch(gla_decay_kernel<bf16>, grid, dim3(256), 0, (cudaStream_t)stream, low, ld, (const bf16*)w2, bias, inv_tau, a, n_tokens, channels, low_rank);
+  HB_CHECK_LAUNCH("gla_decay");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The recurrence.  A block owns 32 value channels of one head of one sequence and walks that
+// sequence's tokens of the step in order; thread (x, y) keeps the state rows y, y + 4, ... of
+// column x in registers.  q, k and the decays of a token pass through shared memory.
+#define GLA_ROWGROUPS 4
+template <int RPT>  // rows per thread: dk <= 4 * RPT
+__global__ void __launch_bounds__(32 * GLA_ROWGROUPS)
+gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
+                float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                float* __restrict__ out, int ldo, int H, int dk, int dv, float qscale) {
+  extern __shared__ float sh[];  // q[dk], k[dk], a[dk], red[GLA_ROWGROUPS][32]
+  float* qs = sh;
+  float* ks = sh + dk;
+  float* as = sh + 2 * dk;
+  float* red = sh + 3 * dk;
+  pdl_wait();
+  pdl_launch();
+  const int b = blockIdx.x, h = blockIdx.y, x = threadIdx.x, y = threadIdx.y;
+  const int col = blockIdx.z * 32 + x, tid = y * 32 + x;
+  const int t0 = seq_start[b], t1 = seq_start[b + 1];
+  float* S = state + (((size_t)seq_slot[b] * H + h) * dk) * (size_t)dv;
+  float s[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int r = y + GLA_ROWGROUPS * i;
+    s[i] = (r < dk && col < dv) ? S[(size_t)r * dv + col] : 0.0f;
+  }
+  for (int t = t0; t < t1; ++t) {
+    const float* row = proj + (size_t)t * ld;
+    for (int i = tid; i < dk; i += 32 * GLA_ROWGROUPS) {
+      qs[i] = row[q_off + h * dk + i] * qscale;
+      ks[i] = row[k_off + h * dk + i];
+      as[i] = decay[(size_t)t * H * dk + h * dk + i];
+    }
+    const float v = col < dv ? row[v_off + h * dv + col] : 0.0f;
+    __syncthreads();
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int r = y + GLA_ROWGROUPS * i;
+      if (r < dk) {
+        s[i] = fmaf(as[r], s[i], ks[r] * v);
+        acc = fmaf(s[i], qs[r], acc);
+      }
+    }
+    red[y * 32 + x] = acc;
+    __syncthreads();
+    if (y == 0 && col < dv) {
+      float o = red[x];
+#pragma unroll
+      for (int g = 1; g < GLA_ROWGROUPS; ++g) o += red[g * 32 + x];
+      out[(size_t)t * ldo + h * dv + col] = o;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int r = y + GLA_ROWGROUPS * i;
+    if (r < dk && col < dv) S[(size_t)r * dv + col] = s[i];
+  }
+}
+
+extern "C" int hb_gla_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay, float* state,
+                           const int* seq_slot, const int* seq_start, float* out, int ldo, int n_seqs, int heads, int dk,
+                           int dv, float qscale, void* stream) {
+  HB_REQUIRE(n_seqs > 0 && heads > 0 && dk > 0 && dv > 0, "gla_scan: sizes must be positive");
+  HB_REQUIRE(dk <= 4 * 64, "gla_scan: %d key channels per head exceed the supported maximum 256", dk);
+  HB_REQUIRE(heads <= 65535 && ceil_div(dv, 32) <= 65535, "gla_scan: too many heads or value channels");
+  dim3 grid(n_seqs, heads, ceil_div(dv, 32)), block(32, GLA_ROWGROUPS);
+  const size_t smem = (size_t)(3 * dk + 32 * GLA_ROWGROUPS) * sizeof(float);
+  cudaStream_t s = (cudaStream_t)stream;
+#define GLA_GO(RPT) \
+  hb_launch(gla_scan_kernel<RPT>, grid, block, smem, s, proj, ld, q_off, k_off, v_off, decay, state, seq_slot, seq_start, out, ldo, heads, dk, dv, qscale)
+  if (dk <= 32) GLA_GO(8); else if (dk <= 64) GLA_GO(16); else if (dk <= 128) GLA_GO(32); else GLA_GO(64);
+#undef GLA_GO
+  HB_CHECK_LAUNCH("gla_scan");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// y[t, h, :] = o / sqrt(mean(o^2) + eps) * w * silu(g[t, h, :]).  One warp per (token, head).
+template <typename T>
+__global__ void gla_output_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ w, float eps,
+                                  const float* __restrict__ gate, int ldg, T* __restrict__ y, int ldy, int n_tokens, int H,
+                                  int dv) {
+  pdl_wait();
+  pdl_launch();
+  const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (unit >= (long long)n_tokens * H) return;
+  const int t = (int)(unit / H), h = (int)(unit % H);
+  const float* orow = o + (size_t)t * ldo + (size_t)h * dv;
+  float ss = 0.0f;
+  for (int d = lane; d < dv; d += 32) ss += orow[d] * orow[d];
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+  const float* g = gate + (size_t)t * ldg + (size_t)h * dv;
+  T* yr = y + (size_t)t * ldy + (size_t)h * dv;
+  for (int d = lane; d < dv; d += 32) {
+    const float gv = g[d];
+    yr[d] = from_f32<T>(((orow[d] * inv) * w[d]) * (gv / (1.0f + expf(-gv))));
+  }
+}
+
+extern "C" int hb_gla_output(int dtype, const float* o, int ldo, const float* w, float eps, const float* gate, int ldg,
+                             void* y, int ldy, int n_tokens, int heads, int dv, void* stream) {
+  HB_REQUIRE(n_tokens > 0 && heads > 0 && dv > 0, "gla_output: sizes must be positive");
+  const long long blocks = ceil_div_ll((long long)n_tokens * heads, 4);
+  HB_REQUIRE(blocks < 2147483647LL, "gla_output: too many (token, head) pairs");
+  if (dtype == HB_F32)
+    hb_launch(gla_output_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, (cudaStream_t)stream, o, ldo, w, eps, gate, ldg, (float*)y, ldy, n_tokens, heads, dv);
+  else
+    hb_launch(gla_output_kernel<bf16>, dim3((unsigned)blocks), dim3(128), 0, (cudaStream_t)stream, o, ldo, w, eps, gate, ldg, (bf16*)y, ldy, n_tokens, heads, dv);
+  HB_CHECK_LAUNCH("gla_output");
+  return 0;
+}

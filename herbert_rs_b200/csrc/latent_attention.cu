@@ -1,0 +1,271 @@
+// Attention over a cached latent: every token stores one vector [c | r] (c: `rank` numbers, normed;
+// r: `rot` numbers, rotated by position) from which all heads' keys and values follow
+// (k_h = [Uk_h c | r], v_h = Uv_h c).  The kernels never build k or v.  With q_h = [a_h | b_h]:
+//
+//   score(t, j) = a_h . (Uk_h c_j) + b_h . r_j = (Uk_h^T a_h) . c_j + b_h . r_j
+//   out_h       = Uv_h (sum_j p_j c_j)
+//
+// so a query becomes one vector of rank + rot numbers (`hb_headwise_gemm` makes Uk_h^T a_h,
+// `hb_rotate_heads` the rotated part), attention runs with ONE key/value "head" shared by all query
+// heads and returns sum_j p_j c_j, and `hb_headwise_gemm` again lifts that to the value size.
+//
+//   softmax     p_j = exp(s_j) / (sum_i exp(s_i) + exp(sink_h)): the sink has no key and no value
+//   range       keys lo..p of the query at position p, lo = max(0, p - window + 1) (window 0: all)
+//   rotation    pair (i, i + rot/2) at position p turns by a = p * f_i; cos a and sin a are both
+//               multiplied by one constant m (frequency scaling folds into f and m on the host)
+//   cache       one plane [pages][page_size][rank + rot] in the activation dtype
+//
+// Scores, softmax, angles and the norm of c are float on both paths.
+#include "api.h"
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// One warp per token: c = RMSNorm(kv[:rank]) * w, r = rotate(kv[rank:]), both into the cache.
+template <typename T>
+__global__ void latent_kv_store_kernel(const float* __restrict__ kv, int ld, const float* __restrict__ nw, float eps,
+                                       const float* __restrict__ freq, float mscale, int rank, int rot,
+                                       const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                       const int* __restrict__ seq_pages, int pages_stride, T* __restrict__ cache,
+                                       int n_tokens, int page_size) {
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= n_tokens) return;
+  const float* row = kv + (size_t)t * ld;
+  float ss = 0.0f;
+  for (int i = lane; i < rank; i += 32) ss += row[i] * row[i];
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
+  const int p = tok_pos[t], b = tok_seq[t];
+  const int page = seq_pages[(size_t)b * pages_stride + p / page_size];
+  T* dst = cache + ((size_t)page * page_size + (p % page_size)) * (size_t)(rank + rot);
+  for (int i = lane; i < rank; i += 32) dst[i] = from_f32<T>((row[i] * inv) * nw[i]);
+  const int half = rot >> 1;
+  for (int i = lane; i < half; i += 32) {
+    float s, c;
+    sincosf((float)p * freq[i], &s, &c);
+    s *= mscale;
+    c *= mscale;
+    const float u = row[rank + i], v = row[rank + half + i];
+    dst[rank + i] = from_f32<T>(u * c - v * s);
+    dst[rank + half + i] = from_f32<T>(v * c + u * s);
+  }
+}
+
+extern "C" int hb_latent_kv_store(int dtype, const float* kv, int ld, const float* norm_w, float eps, const float* freq,
+                                  float mscale, int rank, int rot, const int* tok_seq, const int* tok_pos,
+                                  const int* seq_pages, int pages_stride, void* cache, int n_tokens, int page_size,
+                                  void* stream) {
+  HB_REQUIRE(n_tokens > 0 && rank > 0 && rot >= 0 && rot % 2 == 0 && page_size > 0, "latent_kv_store: bad sizes");
+  HB_REQUIRE(ld >= rank + rot, "latent_kv_store: rows are shorter than rank + rot");
+  const int warps = 4;
+  dim3 grid(ceil_div(n_tokens, warps));
+  if (dtype == HB_F32)
+    hb_launch(latent_kv_store_kernel<float>, grid, dim3(warps * 32), 0, (cudaStream_t)stream, kv, ld, norm_w, eps, freq, mscale, rank,
+              rot, tok_seq, tok_pos, seq_pages, pages_stride, (float*)cache, n_tokens, page_size);
+  else
+    hb_launch(latent_kv_store_kernel<bf16>, grid, dim3(warps * 32), 0, (cudaStream_t)stream, kv, ld, norm_w, eps, freq, mscale, rank,
+              rot, tok_seq, tok_pos, seq_pages, pages_stride, (bf16*)cache, n_tokens, page_size);
+  HB_CHECK_LAUNCH("latent_kv_store");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The rotated part of every head of every token: in[t, h*in_hs + in_off + ..rot] -> out[t, h*out_hs + out_off + ..rot],
+// rotated at the token's position and multiplied by `scale`.  One thread per pair.
+__global__ void rotate_heads_kernel(const float* __restrict__ in, int ld_in, int in_hs, int in_off, float* __restrict__ out,
+                                    int ld_out, int out_hs, int out_off, const float* __restrict__ freq, float mscale,
+                                    const int* __restrict__ tok_pos, int n_tokens, int H, int rot, float scale) {
+  pdl_wait();
+  pdl_launch();
+  const int half = rot >> 1;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n_tokens * H * half) return;
+  const int i = (int)(idx % half), h = (int)((idx / half) % H), t = (int)(idx / ((long long)half * H));
+  float s, c;
+  sincosf((float)tok_pos[t] * freq[i], &s, &c);
+  s *= mscale;
+  c *= mscale;
+  const float* src = in + (size_t)t * ld_in + (size_t)h * in_hs + in_off;
+  float* dst = out + (size_t)t * ld_out + (size_t)h * out_hs + out_off;
+  const float u = src[i], v = src[half + i];
+  dst[i] = (u * c - v * s) * scale;
+  dst[half + i] = (v * c + u * s) * scale;
+}
+
+extern "C" int hb_rotate_heads(const float* in, int ld_in, int in_head_stride, int in_offset, float* out, int ld_out,
+                               int out_head_stride, int out_offset, const float* freq, float mscale, const int* tok_pos,
+                               int n_tokens, int heads, int rot, float scale, void* stream) {
+  HB_REQUIRE(n_tokens > 0 && heads > 0 && rot >= 0 && rot % 2 == 0, "rotate_heads: bad sizes");
+  if (rot == 0) return 0;
+  const long long n = (long long)n_tokens * heads * (rot / 2);
+  hb_launch(rotate_heads_kernel, dim3((unsigned)ceil_div_ll(n, 256)), dim3(256), 0, (cudaStream_t)stream, in, ld_in, in_head_stride,
+            in_offset, out, ld_out, out_head_stride, out_offset, freq, mscale, tok_pos, n_tokens, heads, rot, scale);
+  HB_CHECK_LAUNCH("rotate_heads");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// A product per head:  out[t, h*out_hs + n] = scale * sum_k in[t, h*in_hs + k] * W[h][k][n]   (n < N, k < K)
+// optionally times sigmoid(gate[t, h*N + n]).  W is [H][K][N] with n innermost, so a warp reads W
+// along n.  A block takes HW_TT tokens of one head and keeps their input rows in shared memory: W is
+// read once per HW_TT tokens.
+#define HW_TT 8
+#define HW_THREADS 128
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(HW_THREADS)
+headwise_gemm_kernel(const float* __restrict__ in, int ld_in, int in_hs, const TW* __restrict__ w, TO* __restrict__ out,
+                     int ld_out, int out_hs, const float* __restrict__ gate, int ld_gate, int n_tokens, int K, int N,
+                     float scale) {
+  extern __shared__ float a[];  // [HW_TT][K]
+  pdl_wait();
+  pdl_launch();
+  const int t0 = blockIdx.x * HW_TT, h = blockIdx.y;
+  for (int i = threadIdx.x; i < HW_TT * K; i += HW_THREADS) {
+    const int tt = i / K, k = i % K;
+    a[i] = (t0 + tt < n_tokens) ? in[(size_t)(t0 + tt) * ld_in + (size_t)h * in_hs + k] : 0.0f;
+  }
+  __syncthreads();
+  const TW* wh = w + (size_t)h * K * N;
+  for (int n = blockIdx.z * HW_THREADS + threadIdx.x; n < N; n += gridDim.z * HW_THREADS) {
+    float acc[HW_TT];
+#pragma unroll
+    for (int i = 0; i < HW_TT; ++i) acc[i] = 0.0f;
+    for (int k = 0; k < K; ++k) {
+      const float wv = to_f32(wh[(size_t)k * N + n]);
+#pragma unroll
+      for (int i = 0; i < HW_TT; ++i) acc[i] = fmaf(a[i * K + k], wv, acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < HW_TT; ++i) {
+      const int t = t0 + i;
+      if (t >= n_tokens) break;
+      float v = acc[i] * scale;
+      if (gate) {
+        const float g = gate[(size_t)t * ld_gate + (size_t)h * N + n];
+        v *= 1.0f / (1.0f + expf(-g));
+      }
+      out[(size_t)t * ld_out + (size_t)h * out_hs + n] = from_f32<TO>(v);
+    }
+  }
+}
+
+extern "C" int hb_headwise_gemm(int dtype, int out_dtype, const float* in, int ld_in, int in_head_stride, const void* w,
+                                void* out, int ld_out, int out_head_stride, const float* gate, int ld_gate, int n_tokens,
+                                int heads, int K, int N, float scale, void* stream) {
+  HB_REQUIRE(n_tokens > 0 && heads > 0 && K > 0 && N > 0, "headwise_gemm: sizes must be positive");
+  HB_REQUIRE(heads <= 65535, "headwise_gemm: at most 65535 heads");
+  const size_t smem = (size_t)HW_TT * K * sizeof(float);
+  HB_REQUIRE(smem <= 48 * 1024, "headwise_gemm: K = %d exceeds what a block keeps in shared memory", K);
+  dim3 grid(ceil_div(n_tokens, HW_TT), heads, ceil_div(N, HW_THREADS));
+  cudaStream_t s = (cudaStream_t)stream;
+#define HW_GO(TW, TO)                                                                                                           \
+  hb_launch(headwise_gemm_kernel<TW, TO>, grid, dim3(HW_THREADS), smem, s, in, ld_in, in_head_stride, (const TW*)w, (TO*)out, \
+            ld_out, out_head_stride, gate, ld_gate, n_tokens, K, N, scale)
+  if (dtype == HB_F32) {
+    HB_REQUIRE(out_dtype == HB_F32, "headwise_gemm: the 32-bit path writes floats");
+    HW_GO(float, float);
+  } else if (out_dtype == HB_F32) {
+    HW_GO(bf16, float);
+  } else {
+    HW_GO(bf16, bf16);
+  }
+#undef HW_GO
+  HB_CHECK_LAUNCH("headwise_gemm");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// One warp per (token, head), 32 keys at a time (a lane per key for the scores, a lane per channel
+// for the sum).  q: [T][H][rank + rot] floats, already scaled.  out: [T][H][rank] floats.  The online
+// softmax starts from the sink as if it were a first key with value zero: m = sink, l = 1.
+#define LA_WARPS 4
+template <typename T, int CH>  // CH = ceil(rank / 32)
+__global__ void __launch_bounds__(LA_WARPS * 32)
+latent_attention_kernel(const float* __restrict__ q, int ldq, float* __restrict__ out, int ldo, const T* __restrict__ cache,
+                        const float* __restrict__ sink, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                        const int* __restrict__ seq_pages, int pages_stride, int n_tokens, int H, int rank, int rot,
+                        int page_size, int window) {
+  extern __shared__ float qs[];  // [LA_WARPS][rank + rot]
+  pdl_wait();
+  pdl_launch();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, W = rank + rot;
+  const long long unit = (long long)blockIdx.x * LA_WARPS + warp;
+  if (unit >= (long long)n_tokens * H) return;
+  const int t = (int)(unit / H), h = (int)(unit % H);
+  const int p = tok_pos[t], b = tok_seq[t];
+  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  float* qw = qs + (size_t)warp * W;
+  const float* qp = q + (size_t)t * ldq + (size_t)h * W;
+  for (int d = lane; d < W; d += 32) qw[d] = qp[d];
+  __syncwarp();
+  const int* pages = seq_pages + (size_t)b * pages_stride;
+
+  float m = sink ? sink[h] : -INFINITY, l = sink ? 1.0f : 0.0f;
+  float o[CH];
+#pragma unroll
+  for (int i = 0; i < CH; ++i) o[i] = 0.0f;
+
+  for (int j0 = lo; j0 <= p; j0 += 32) {
+    const int j = j0 + lane;
+    float s = -INFINITY;
+    if (j <= p) {
+      const T* kr = cache + ((size_t)pages[j / page_size] * page_size + (j % page_size)) * (size_t)W;
+      float dot = 0.0f;
+      for (int d = 0; d < W; ++d) dot = fmaf(qw[d], to_f32(kr[d]), dot);
+      s = dot;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);
+    const float pj = (j <= p) ? expf(s - m_new) : 0.0f;
+    l = l * corr + warp_sum(pj);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < CH; ++i) o[i] *= corr;
+    const int nk = (p - j0 + 1 < 32) ? p - j0 + 1 : 32;
+    for (int k = 0; k < nk; ++k) {
+      const float pk = __shfl_sync(0xffffffffu, pj, k);
+      const int jk = j0 + k;
+      const T* vr = cache + ((size_t)pages[jk / page_size] * page_size + (jk % page_size)) * (size_t)W;
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const int d = lane + 32 * i;
+        if (d < rank) o[i] = fmaf(pk, to_f32(vr[d]), o[i]);
+      }
+    }
+  }
+  const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+  float* op = out + (size_t)t * ldo + (size_t)h * rank;
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int d = lane + 32 * i;
+    if (d < rank) op[d] = o[i] * inv;
+  }
+}
+
+extern "C" int hb_latent_attention(int dtype, const float* q, int ldq, float* out, int ldo, const void* cache,
+                                   const float* sink, const int* tok_seq, const int* tok_pos, const int* seq_pages,
+                                   int pages_stride, int n_tokens, int heads, int rank, int rot, int page_size, int window,
+                                   void* stream) {
+  HB_REQUIRE(n_tokens > 0 && heads > 0 && rank > 0 && rot >= 0 && page_size > 0 && window >= 0, "latent_attention: bad sizes");
+  HB_REQUIRE(rank <= 1024, "latent_attention: latent size %d exceeds the supported maximum 1024", rank);
+  const size_t smem = (size_t)LA_WARPS * (rank + rot) * sizeof(float);
+  HB_REQUIRE(smem <= 48 * 1024, "latent_attention: rank + rot = %d exceeds what a block keeps in shared memory", rank + rot);
+  const long long blocks = ceil_div_ll((long long)n_tokens * heads, LA_WARPS);
+  HB_REQUIRE(blocks < 2147483647LL, "latent_attention: too many (token, head) pairs");
+  cudaStream_t s = (cudaStream_t)stream;
+#define LA_GO(T, CH)                                                                                                              \
+  hb_launch(latent_attention_kernel<T, CH>, dim3((unsigned)blocks), dim3(LA_WARPS * 32), smem, s, q, ldq, out, ldo, (const T*)cache, \
+            sink, tok_seq, tok_pos, seq_pages, pages_stride, n_tokens, heads, rank, rot, page_size, window)
+  const int ch = ceil_div(rank, 32);
+  if (dtype == HB_F32) {
+    if (ch <= 2) LA_GO(float, 2); else if (ch <= 4) LA_GO(float, 4); else if (ch <= 8) LA_GO(float, 8);
+    else if (ch <= 16) LA_GO(float, 16); else LA_GO(float, 32);
+  } else {
+    if (ch <= 2) LA_GO(bf16, 2); else if (ch <= 4) LA_GO(bf16, 4); else if (ch <= 8) LA_GO(bf16, 8);
+    else if (ch <= 16) LA_GO(bf16, 16); else LA_GO(bf16, 32);
+  }
+#undef LA_GO
+  HB_CHECK_LAUNCH("latent_attention");
+  return 0;
+}

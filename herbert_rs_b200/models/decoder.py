@@ -97,7 +97,7 @@ class DecoderModel:
         ws = self.rt.workspace
         ws.rewind()
         x = ws.take((batch.n_tokens, self.spec.hidden_size), torch.float32)
-        ops.embed(self.embed, batch.token_ids, x)
+        ops.embed(self.embed, batch.token_ids, x, self.spec.embedding_scale)
         # a block may begin the first norm of the block that runs after it (parts/base.py)
         sched, pending = self.spec.schedule, None
         for i, st in enumerate(sched):

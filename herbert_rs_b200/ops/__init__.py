@@ -18,6 +18,8 @@ from . import lib as _libmod
 from .options import KernelOptions
 
 F32, BF16 = 0, 1
+ACT_SILU, ACT_GELU_TANH, ACT_GELU = 0, 1, 2
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "gelu": ACT_GELU}
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
 SKINNY_MAX_ROWS = 64
 # The one place where a choice between kernels can be changed (by a measurement script or a test
@@ -25,9 +27,9 @@ SKINNY_MAX_ROWS = 64
 options = KernelOptions()
 
 _SIGS = {
-    "hb_embed": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "hb_embed": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "hb_rmsnorm": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
-    "hb_swiglu": [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_swiglu": [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_add_residual": [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "hb_qk_norm_rope_cache": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                               c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -66,6 +68,24 @@ _SIGS = {
     "hb_rng_normal": [c_int, c_void_p, ctypes.c_longlong, ctypes.c_ulonglong, c_float, c_float, c_void_p],
     "hb_fill": [c_int, c_void_p, ctypes.c_longlong, c_float, c_void_p],
     "hb_cast": [c_int, c_void_p, c_int, c_void_p, ctypes.c_longlong, c_int, c_void_p],
+    "hb_layernorm": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    "hb_layernorm_residual": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    "hb_latent_kv_store": [c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p,
+                           c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+    "hb_rotate_heads": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int,
+                        c_int, c_int, c_float, c_void_p],
+    "hb_headwise_gemm": [c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                         c_int, c_int, c_int, c_float, c_void_p],
+    "hb_latent_attention": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_gla_decay": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+    "hb_gla_scan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                    c_int, c_int, c_int, c_float, c_void_p],
+    "hb_gla_output": [c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                      c_void_p],
+    "hb_moe_route": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_moe_experts": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                       c_int, c_int, c_int, c_int, c_int, c_void_p],
 }
 _fns: dict = {}
 
@@ -85,7 +105,7 @@ def _fn(name: str):
 
 
 # kernels each launcher starts (for honest launch counts)
-_KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2, "hb_argmax": 2, "hb_sample": 2}
+_KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2, "hb_argmax": 2, "hb_sample": 2, "hb_moe_experts": 2}
 _launches = 0
 
 
@@ -264,11 +284,131 @@ def cast(src: torch.Tensor, dtype: torch.dtype, round_bf16: bool = False) -> tor
     return out
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, :] = float(table[ids[t], :]); out is the float residual stream [T, H]."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t, :] = float(table[ids[t], :]) * scale; out is the float residual stream [T, H]."""
     _check(table, None, "table"); _check(ids, torch.int32, "ids"); _check(out, torch.float32, "out")
     _run("hb_embed", dtype_code(table.dtype), table.data_ptr(), ids.data_ptr(), out.data_ptr(),
-         ids.numel(), table.shape[1], table.shape[0], _stream())
+         ids.numel(), table.shape[1], table.shape[0], float(scale), _stream())
+
+
+def to_activation(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x (float, contiguous) in out's dtype, rounded to nearest even: what a sublayer that reads
+    the residual stream itself gets on the bfloat16 path."""
+    _check(x, torch.float32, "x"); _check(out, None, "out")
+    if not (x.is_contiguous() and out.is_contiguous() and x.numel() == out.numel()):
+        raise BackendError("to_activation: x and out must be contiguous and of one size")
+    _run("hb_cast", 0, x.data_ptr(), dtype_code(out.dtype), out.data_ptr(), x.numel(), 0, _stream())
+
+
+def layernorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
+    """out[r] = (x - mean) / sqrt(var + eps) * w of row rows[r] (or r) of x; x and w float."""
+    _check(x, torch.float32, "x"); _check(w, torch.float32, "w"); _check(out, None, "out")
+    _run("hb_layernorm", dtype_code(out.dtype), x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(rows),
+         out.shape[0], x.shape[-1], float(eps), _stream())
+
+
+def layernorm_residual(y: torch.Tensor, w: torch.Tensor, scale: torch.Tensor | None, x: torch.Tensor,
+                       h: torch.Tensor | None, eps: float, dtype: torch.dtype) -> None:
+    """x += layernorm(y) * w * scale (scale may be None); h, if given, receives the updated x in the
+    activation dtype `dtype`."""
+    _check(y, torch.float32, "y"); _check(w, torch.float32, "w"); _check(x, torch.float32, "x")
+    if h is not None:
+        _check(h, dtype, "h")
+    if not x.is_contiguous() or (h is not None and not h.is_contiguous()):
+        raise BackendError("layernorm_residual: x and h must be contiguous")
+    _run("hb_layernorm_residual", dtype_code(dtype), y.data_ptr(), y.stride(0), w.data_ptr(), _ptr(scale), x.data_ptr(),
+         _ptr(h), x.shape[0], x.shape[1], float(eps), _stream())
+
+
+def latent_kv_store(kv, norm_w, eps, freq, mscale, rank, rot, tok_seq, tok_pos, seq_pages, cache, page_size) -> None:
+    """Rows [c | r] of kv (float, [T, >= rank + rot]): c normed (RMS, weight norm_w), r rotated at the
+    token's position; both stored at the token's place of the one-plane paged cache."""
+    _check(kv, torch.float32, "kv"); _check(norm_w, torch.float32, "norm_w"); _check(freq, torch.float32, "freq")
+    _run("hb_latent_kv_store", dtype_code(cache.dtype), kv.data_ptr(), kv.stride(0), norm_w.data_ptr(), float(eps),
+         freq.data_ptr(), float(mscale), int(rank), int(rot), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_pages.data_ptr(),
+         seq_pages.stride(0), cache.data_ptr(), kv.shape[0], int(page_size), _stream())
+
+
+def rotate_heads(src, src_head_stride, src_offset, out, out_head_stride, out_offset, freq, mscale, tok_pos, heads, rot,
+                 scale=1.0) -> None:
+    """out[t, h*out_head_stride + out_offset + ..rot] = scale * rotation of src[t, h*src_head_stride + src_offset + ..rot]
+    at position tok_pos[t] (pairs (i, i + rot/2), angle p * freq[i], cos and sin times mscale)."""
+    _check(src, torch.float32, "src"); _check(out, torch.float32, "out"); _check(freq, torch.float32, "freq")
+    _run("hb_rotate_heads", src.data_ptr(), src.stride(0), int(src_head_stride), int(src_offset), out.data_ptr(), out.stride(0),
+         int(out_head_stride), int(out_offset), freq.data_ptr(), float(mscale), tok_pos.data_ptr(), src.shape[0], int(heads),
+         int(rot), float(scale), _stream())
+
+
+def headwise_gemm(src, src_head_stride, w, out, out_head_stride, scale=1.0, gate=None) -> None:
+    """out[t, h*out_head_stride + n] = scale * sum_k src[t, h*src_head_stride + k] * w[h, k, n], times
+    sigmoid(gate[t, h*N + n]) if a gate (float) is given.  src float; w [H, K, N] in the compute dtype; out
+    float or the compute dtype."""
+    _check(src, torch.float32, "src"); _check(w, None, "w"); _check(out, None, "out")
+    if not w.is_contiguous() or w.dim() != 3:
+        raise BackendError("headwise_gemm: w must be a contiguous [heads, K, N] tensor")
+    if gate is not None:
+        _check(gate, torch.float32, "gate")
+    H, K, N = w.shape
+    _run("hb_headwise_gemm", dtype_code(w.dtype), dtype_code(out.dtype), src.data_ptr(), src.stride(0), int(src_head_stride),
+         w.data_ptr(), out.data_ptr(), out.stride(0), int(out_head_stride), _ptr(gate), 0 if gate is None else gate.stride(0),
+         src.shape[0], H, K, N, float(scale), _stream())
+
+
+def latent_attention(q, out, cache, sink, tok_seq, tok_pos, seq_pages, heads, rank, rot, page_size, window) -> None:
+    """out[t, h, :rank] = sum_j p_j c_j over the cached rows [c_j | r_j] that the token may see, with
+    scores q[t, h, :] . [c_j | r_j] (q float, already scaled) and a softmax whose denominator also holds
+    exp(sink[h]) when a sink is given."""
+    _check(q, torch.float32, "q"); _check(out, torch.float32, "out")
+    if sink is not None:
+        _check(sink, torch.float32, "sink")
+    _run("hb_latent_attention", dtype_code(cache.dtype), q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
+         cache.data_ptr(), _ptr(sink), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0),
+         q.shape[0], int(heads), int(rank), int(rot), int(page_size), int(window or 0), _stream())
+
+
+def gla_decay(low, w2, bias, tau, out) -> None:
+    """out[t, c] = sigmoid(z)^(1/tau) with z = bias[c] + low[t, :] . w2[c, :]; low and out float."""
+    _check(low, torch.float32, "low"); _check(w2, None, "w2"); _check(out, torch.float32, "out")
+    _run("hb_gla_decay", dtype_code(w2.dtype), low.data_ptr(), low.stride(0), w2.data_ptr(), _ptr(bias), 1.0 / float(tau),
+         out.data_ptr(), low.shape[0], w2.shape[0], w2.shape[1], _stream())
+
+
+def gla_scan(proj, q_off, k_off, v_off, decay, state, seq_slot, seq_start, out, n_seqs, heads, dk, dv, qscale) -> None:
+    """The recurrence S = diag(a) S + k v^T, o = S^T (q * qscale) over every sequence's tokens of the step, in
+    order, from and into state[slot] ([slots, heads, dk, dv] float).  q, k, v are column ranges of proj."""
+    _check(proj, torch.float32, "proj"); _check(decay, torch.float32, "decay"); _check(state, torch.float32, "state")
+    _check(out, torch.float32, "out")
+    if not (state.is_contiguous() and decay.is_contiguous()):
+        raise BackendError("gla_scan: state and decay must be contiguous")
+    _run("hb_gla_scan", proj.data_ptr(), proj.stride(0), int(q_off), int(k_off), int(v_off), decay.data_ptr(), state.data_ptr(),
+         seq_slot.data_ptr(), seq_start.data_ptr(), out.data_ptr(), out.stride(0), int(n_seqs), int(heads), int(dk), int(dv),
+         float(qscale), _stream())
+
+
+def gla_output(o, w, eps, gate, out, heads, dv) -> None:
+    """out[t, h, :] = rmsnorm(o[t, h, :]) * w * silu(gate[t, h, :]); o and gate float, out in the activation dtype."""
+    _check(o, torch.float32, "o"); _check(w, torch.float32, "w"); _check(gate, torch.float32, "gate"); _check(out, None, "out")
+    _run("hb_gla_output", dtype_code(out.dtype), o.data_ptr(), o.stride(0), w.data_ptr(), float(eps), gate.data_ptr(),
+         gate.stride(0), out.data_ptr(), out.stride(0), o.shape[0], int(heads), int(dv), _stream())
+
+
+def moe_route(h, w_router, ids, weights, top, renorm=False) -> None:
+    """ids[t, :top], weights[t, :top]: the `top` largest of softmax(w_router h[t]) over all experts (ties to
+    the lower index), the weights being those softmax values (divided by their sum with `renorm`)."""
+    _check(h, None, "h"); _check(w_router, h.dtype, "w_router"); _check(ids, torch.int32, "ids"); _check(weights, torch.float32, "weights")
+    _run("hb_moe_route", dtype_code(h.dtype), h.data_ptr(), h.stride(0), w_router.data_ptr(), ids.data_ptr(), weights.data_ptr(),
+         h.shape[0], h.shape[1], w_router.shape[0], int(top), 1 if renorm else 0, _stream())
+
+
+def moe_experts(h, up, down, ids, weights, mid, y, act, accumulate=False) -> None:
+    """y[t] (+)= sum_r weights[t, r] * down[e] act(up[e] h[t]), e = ids[t, r]; up [E, F, D], down [E, D, F] in
+    h's dtype; mid [T * top, F] scratch in h's dtype; y float."""
+    _check(h, None, "h"); _check(up, h.dtype, "up"); _check(down, h.dtype, "down"); _check(mid, h.dtype, "mid"); _check(y, torch.float32, "y")
+    if not (up.is_contiguous() and down.is_contiguous() and mid.is_contiguous()):
+        raise BackendError("moe_experts: up, down and mid must be contiguous")
+    _run("hb_moe_experts", dtype_code(h.dtype), h.data_ptr(), h.stride(0), up.data_ptr(), down.data_ptr(), ids.data_ptr(),
+         weights.data_ptr(), mid.data_ptr(), y.data_ptr(), y.stride(0), h.shape[0], h.shape[1], up.shape[1], ids.shape[1],
+         int(act), 1 if accumulate else 0, _stream())
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
@@ -279,11 +419,11 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, row
          n, x.shape[-1], float(eps), _stream())
 
 
-def swiglu(gu: torch.Tensor, out: torch.Tensor, interleave: int) -> None:
-    """out[t, i] = silu(gate) * up from gu [T, 2I] (see the kernel for the column layout)."""
+def swiglu(gu: torch.Tensor, out: torch.Tensor, interleave: int, act: int = ACT_SILU) -> None:
+    """out[t, i] = act(gate) * up from gu [T, 2I] (see the kernel for the column layout); act: ACT_*."""
     _check(gu, None, "gu"); _check(out, gu.dtype, "out")
     _run("hb_swiglu", dtype_code(gu.dtype), gu.data_ptr(), gu.stride(0), out.data_ptr(), out.stride(0),
-         gu.shape[0], out.shape[1], int(interleave), _stream())
+         gu.shape[0], out.shape[1], int(interleave), int(act), _stream())
 
 
 def add_residual(residual: torch.Tensor, y: torch.Tensor) -> None:

@@ -1,11 +1,16 @@
 """Parts of a layer.  Importing this package registers the built-in kinds."""
 
 from .base import Block, FeedForward, Mixer, Norm, ParamSpec, Part
-from .norm import RMSNorm
-from .rope import RotaryEncoding, rope_tables
+from .norm import LayerNorm, RMSNorm
+from .rope import RotaryEncoding, ScaledRotary, rope_tables, scaled_frequencies
 from .attention import AttentionMixer
+from .latent_attention import LatentAttentionMixer
+from .gla import GatedLinearAttentionMixer
 from .swiglu import SwiGLU, join_gate_up
-from .block import PreNormBlock
+from .moe import RoutedFeedForward
+from .block import PreNormBlock, SublayerNormBlock
 
 __all__ = ["Block", "FeedForward", "Mixer", "Norm", "ParamSpec", "Part", "RMSNorm", "RotaryEncoding",
-           "rope_tables", "AttentionMixer", "SwiGLU", "join_gate_up", "PreNormBlock"]
+           "rope_tables", "AttentionMixer", "SwiGLU", "join_gate_up", "PreNormBlock", "LayerNorm", "ScaledRotary",
+           "scaled_frequencies", "LatentAttentionMixer", "GatedLinearAttentionMixer", "RoutedFeedForward",
+           "SublayerNormBlock"]

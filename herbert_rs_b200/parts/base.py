@@ -39,12 +39,14 @@ class ParamSpec:
     role "matrix": kept in the compute dtype (bfloat16 as stored; widened exactly on the 32-bit
     path).  role "vector": small per-channel weights, kept in float32 on both paths (a tensor
     stored in 32-bit stays so; a bfloat16 one widens exactly).  role "table": integers, int32.
-    init: "normal" = N(0, 0.02); "ones_noise" = 1 + N(0, 0.1); "zeros".
+    init: "normal" = N(0, 0.02); "ones_noise" = 1 + N(0, 0.1); "wide" = N(0, 1); "zeros".
+    A shape entry of -1 is a size that only the stored tensor gives (random weights take `free_size`).
     """
 
     shape: tuple
     role: str = "matrix"
     init: str = "normal"
+    free_size: int = 16
 
 
 class Part:
@@ -55,6 +57,10 @@ class Part:
     graph_safe = True
     # True if forward() accepts an ops.PendingNorm as its input and a `next_norm` keyword.
     shares_norms = False
+    # True if forward() takes the keyword `accumulate`: with accumulate=False a mixer or feed-forward
+    # stores its result into the float array it is given instead of adding to it (a block that
+    # norms a sublayer's result before the residual sum asks for that).
+    can_store = False
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {}

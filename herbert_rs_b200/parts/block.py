@@ -3,9 +3,12 @@
 
 from __future__ import annotations
 
+import torch
+
 from .. import ops
+from ..errors import ConfigError
 from ..registry import build_part, register_part
-from .base import Block
+from .base import Block, ParamSpec
 
 
 class PreNormBlock(Block):
@@ -73,4 +76,87 @@ class PreNormBlock(Block):
         return None
 
 
+class SublayerNormBlock(Block):
+    """x += s1 * norm1(mixer(x)); x += s2 * norm2(ffn(x)): the sublayers read the residual stream
+    itself (its rounding to the activation dtype on the bfloat16 path), their results are normed (a
+    layer norm) and multiplied channel by channel by a stored scale before they join the stream.
+    The spec may leave out the scales (`layer_scale` None) and the feed-forward (`ffn` None).  Norm,
+    scale and sum are one kernel, which also hands the next sublayer its input."""
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.norm1 = build_part("norm", spec.norm1, rt=rt)
+        self.mixer = build_part("mixer", spec.mixer, rt=rt)
+        self.ffn = build_part("ffn", spec.ffn, rt=rt) if spec.ffn is not None else None
+        self.norm2 = build_part("norm", spec.norm2, rt=rt) if self.ffn is not None else None
+        self._names = dict(spec.names)
+        self.scale_names = tuple(spec.layer_scale) if spec.layer_scale else None
+        self.scale1 = self.scale2 = None
+        for part in (self.mixer, self.ffn):
+            if part is not None and not part.can_store:
+                raise ConfigError(f"{type(part).__name__} cannot store its result apart from the residual stream, "
+                                  "which a block that norms a sublayer's result needs")
+        for norm in (spec.norm1, spec.norm2):
+            if norm.kind != "layernorm":
+                raise ConfigError("the block that norms a sublayer's result applies a layer norm")
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for _, p in self.children())
+
+    def children(self):
+        parts = [("norm1", self.norm1), ("mixer", self.mixer)]
+        if self.ffn is not None:
+            parts += [("norm2", self.norm2), ("ffn", self.ffn)]
+        return tuple(parts)
+
+    def _key(self, local, name):
+        prefix = self._names[local]
+        return f"{prefix}.{name}" if prefix else name
+
+    def param_specs(self):
+        out = {}
+        for local, part in self.children():
+            for name, ps in part.param_specs().items():
+                out[self._key(local, name)] = ps
+        if self.scale_names:
+            dim = self.spec.norm1.dim
+            out[self.scale_names[0]] = ParamSpec((dim,), role="vector", init="ones_noise")
+            if self.ffn is not None:
+                out[self.scale_names[1]] = ParamSpec((dim,), role="vector", init="ones_noise")
+        return out
+
+    def load(self, tensors):
+        for local, part in self.children():
+            part.load({name: tensors[self._key(local, name)] for name in part.param_specs()})
+        if self.scale_names:
+            self.scale1 = tensors[self.scale_names[0]].contiguous()
+            if self.ffn is not None:
+                self.scale2 = tensors[self.scale_names[1]].contiguous()
+
+    def weight_bytes(self):
+        return sum(p.weight_bytes() for _, p in self.children()) + (8 * self.spec.norm1.dim if self.scale_names else 0)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, x, batch, cache, normed=None, next_norm=None):
+        ws, dtype = self.rt.workspace, self.rt.dtype
+        wide = dtype == torch.float32
+        if wide:
+            h = x
+        else:
+            h = ws.take(x.shape, dtype)
+            ops.to_activation(x, h)
+        y = ws.take(x.shape, torch.float32)
+        self.mixer.forward(h, y, batch, cache, accumulate=False)
+        h2 = None if (wide or self.ffn is None) else ws.take(x.shape, dtype)
+        ops.layernorm_residual(y, self.norm1.weight, self.scale1, x, h2, self.norm1.eps, dtype)
+        if self.ffn is not None:
+            self.ffn.forward(x if wide else h2, y, batch, accumulate=False)
+            ops.layernorm_residual(y, self.norm2.weight, self.scale2, x, None, self.norm2.eps, dtype)
+        return None
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "sublayer_norm", SublayerNormBlock)

@@ -1,5 +1,5 @@
 """RMSNorm: y = (x / sqrt(mean(x^2) + eps)) * w, in float
-(crates/backends/backend_common/src/kernels.rs:54-64)."""
+(crates/backends/backend_common/src/kernels.rs:54-64), and the layer norm with a weight and no bias."""
 
 from __future__ import annotations
 
@@ -11,13 +11,14 @@ from .base import Norm, ParamSpec
 class RMSNorm(Norm):
     def __init__(self, spec, rt):
         self.dim, self.eps, self.rt = spec.dim, spec.eps, rt
+        self.name = getattr(spec, "weight_name", "weight")
         self.weight = None
 
     def param_specs(self):
-        return {"weight": ParamSpec((self.dim,), role="vector", init="ones_noise")}
+        return {self.name: ParamSpec((self.dim,), role="vector", init="ones_noise")}
 
     def load(self, tensors):
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.name].contiguous()
 
     def weight_bytes(self):
         return self.dim * 4
@@ -29,4 +30,15 @@ class RMSNorm(Norm):
         return (self.weight, self.eps)
 
 
+class LayerNorm(RMSNorm):
+    """y = (x - mean(x)) / sqrt(var(x) + eps) * w, no bias, in float (var: mean of squared deviations)."""
+
+    def forward(self, x, out, rows=None):
+        ops.layernorm(x, self.weight, out, self.eps, rows)
+
+    def shareable(self):
+        return None         # the products' shared norm is the RMS form only
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)

@@ -42,4 +42,32 @@ class RotaryEncoding(Part):
         self.cos, self.sin = _TABLES[key]
 
 
+def scaled_frequencies(spec):
+    """(f [rotary_dim/2] float64, m) of a `ScaledRotarySpec` (its docstring has the formulas)."""
+    import math
+    half = spec.rotary_dim // 2
+    i = torch.arange(half, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * i / spec.rotary_dim)
+    if spec.factor is None:
+        return f, 1.0
+
+    def d(t):
+        return spec.rotary_dim * math.log(spec.original / (2.0 * math.pi * t)) / (2.0 * math.log(spec.theta))
+    lo = max(math.floor(d(spec.fast)), 0)
+    hi = min(math.ceil(d(spec.slow)), spec.rotary_dim - 1)
+    r = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return f / spec.factor * r + f * (1.0 - r), 0.1 * math.log(spec.factor) + 1.0
+
+
+class ScaledRotary(Part):
+    """Frequencies on the device (float32) and the constant that multiplies cos and sin; the kernels
+    take the angle position * frequency in float, so no table bounds the position."""
+
+    def __init__(self, spec, rt):
+        self.rotary_dim = spec.rotary_dim
+        f, self.mscale = scaled_frequencies(spec)
+        self.freq = f.to(torch.float32).to(rt.device)
+
+
 register_part("position", "rope", RotaryEncoding)
+register_part("position", "scaled_rope", ScaledRotary)

@@ -53,10 +53,12 @@ def architectures() -> list:
 
 
 def architecture_for(config_json: dict) -> str:
-    """The registered architecture name chosen by config.json's `architectures`, else `model_type`,
-    else the registered default."""
+    """The registered architecture name chosen by config.json's `architectures` (a list) or
+    `architecture` (one name), else `model_type`, else the registered default."""
     archs = config_json.get("architectures")
     names = [a for a in archs if isinstance(a, str)] if isinstance(archs, list) else []
+    if isinstance(config_json.get("architecture"), str):
+        names.append(config_json["architecture"])
     for a in names:
         if a in _ARCHITECTURES:
             return a

@@ -46,7 +46,7 @@ def check_tensors(model, files) -> None:
         if name not in have:
             continue
         dtype, shape = files.info(name)
-        if tuple(shape) != tuple(ps.shape):
+        if len(shape) != len(ps.shape) or any(w != -1 and int(g) != int(w) for g, w in zip(shape, ps.shape)):
             wrong_shape.append(f"{name}: expected {list(ps.shape)}, got {list(shape)}")
         if ps.role in ("matrix", "vector") and dtype not in _FLOAT_STORED:
             wrong_dtype.append(f"{name}: stored as {dtype}, need F32, BF16 or F16")

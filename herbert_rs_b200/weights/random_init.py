@@ -24,12 +24,14 @@ from . import counter_rng
 from .loader import build_model, fill_model
 from .safetensors_io import save_stream
 
-_INIT = {"normal": (0.0, 0.02), "ones_noise": (1.0, 0.1)}
+_INIT = {"normal": (0.0, 0.02), "ones_noise": (1.0, 0.1), "wide": (0.0, 1.0)}
 
 
 def random_tensor(name: str, ps, seed: int, device="cpu") -> torch.Tensor:
     """The tensor `name` of a random model, as bfloat16 values (int32 for tables), on `device`."""
     device = torch.device(device)
+    if any(d == -1 for d in ps.shape):
+        ps = type(ps)(tuple(ps.free_size if d == -1 else d for d in ps.shape), ps.role, ps.init, ps.free_size)
     if ps.role == "table":
         return torch.zeros(ps.shape, dtype=torch.int32, device=device)
     if ps.init == "zeros":
@@ -62,7 +64,8 @@ def write_random_model(config_json: dict, out_dir: str, seed: int = 0, device="c
     with open(os.path.join(out_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(full, f, indent=1)
     specs = model.param_specs()
-    entries = [(name, torch.int32 if ps.role == "table" else torch.bfloat16, tuple(ps.shape),
+    entries = [(name, torch.int32 if ps.role == "table" else torch.bfloat16,
+                tuple(ps.free_size if d == -1 else d for d in ps.shape),
                 (lambda name=name, ps=ps: random_tensor(name, ps, seed, device))) for name, ps in specs.items()]
     save_stream(entries, os.path.join(out_dir, "model.safetensors"), metadata={"format": "pt", "seed": seed})
     return out_dir
