@@ -191,6 +191,167 @@ def fp32_check(cfg: dict, bf16_engine, n_tokens: int = 64) -> dict:
             "largest_logit_given_up": round(float(lost.max()), 5)}
 
 
+# ---- the Kebisun design beside the dense decoder at equal sizes ---------------------------------------
+def _kebisun_config(width, heads, dim, rot, vdim, kv_rank, q_rank, window, gla_heads, gla_dk, gla_dv, ff, experts, top, expert_ff,
+                    vocab, decay_rank=32):
+    latent = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,
+              "scale": (dim + rot) ** -0.5, "mask": {"size": window},
+              "rot": {"base": 10000.0, "dims": rot, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    gla = {"heads": gla_heads, "dim": gla_dk, "vdim": gla_dv, "tau": 16.0, "decay_rank": decay_rank}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+    layers = [{"type": "latent_attention", "mixer": latent, "mlp": dense}, {"type": "gla", "mixer": gla, "mlp": moe},
+              {"type": "latent_attention", "mixer": latent, "mlp": moe}, {"type": "gla", "mixer": gla, "mlp": dense}]
+    return {"architecture": "Kebisun", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "layers": layers}
+
+
+DESIGN_SIZES = {
+    # Kebisun layer sizes, and the dense decoder of the same width, depth and feed-forward width beside them
+    "1k": (dict(width=1024, heads=8, dim=64, rot=32, vdim=64, kv_rank=256, q_rank=384, window=4096, gla_heads=4, gla_dk=128,
+                gla_dv=256, ff=3072, experts=16, top=2, expert_ff=768, vocab=32000),
+           dict(hidden_size=1024, num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=4, head_dim=128,
+                intermediate_size=3072, vocab_size=32000, eos_token_id=31999)),
+    "2k": (dict(width=2048, heads=16, dim=128, rot=64, vdim=128, kv_rank=512, q_rank=768, window=4096, gla_heads=4, gla_dk=256,
+                gla_dv=512, ff=8192, experts=32, top=4, expert_ff=1408, vocab=32000),
+           dict(hidden_size=2048, num_hidden_layers=4, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+                intermediate_size=8192, vocab_size=32000, eos_token_id=31999)),
+}
+
+
+def _launcher_work(name, n, ctx):
+    """(FLOPs, bytes) that all `n` launches of a launcher do in one step of `ctx` (a dict of the step's
+    and the model's sizes), for the launchers compared between the two models; None for the others."""
+    T, L, B = ctx["tokens"], ctx["kv_len"], ctx["seqs"]
+    pairs = T * (L - (T // B - 1) / 2.0) if T > B else T * L        # (query, key) pairs per head: causal prompt / one query over L keys
+    es = 2
+    if ctx["kind"] == "kebisun":
+        H, rk, dr, dn, dv, D = ctx["heads"], ctx["kv_rank"], ctx["rot"], ctx["dim"], ctx["vdim"], ctx["width"]
+        if name == "hb_latent_attention":
+            per = n / 1.0
+            return per * 2.0 * pairs * H * (2 * rk + dr), per * (B * L * (rk + dr) * es + T * H * (2 * rk + dr) * 4)
+        if name == "hb_headwise_gemm":      # two per latent layer: dn -> rk and rk -> dv
+            per = n / 2.0
+            return per * 2.0 * T * H * rk * (dn + dv), per * (H * rk * (dn + dv) * es + T * H * (rk + dn + dr + rk + dv) * 4)
+        if name == "hb_layernorm_residual":
+            return n * 8.0 * T * D, n * T * D * (4 + 4 + 4 + es)
+        if name == "hb_gla_scan":
+            gh, dk, gv = ctx["gla_heads"], ctx["gla_dk"], ctx["gla_dv"]
+            return n * 4.0 * T * gh * dk * gv, n * (T * gh * (3 * dk + 2 * gv) * 4 + 2 * B * gh * dk * gv * 4)
+        if name == "hb_moe_experts":
+            E, top, F = ctx["experts"], ctx["top"], ctx["expert_ff"]
+            return n * 4.0 * T * top * F * D, n * (min(E, T * top) * 2 * F * D * es + T * D * (es + 4))
+    else:
+        H, KV, hd, D = ctx["heads"], ctx["kv_heads"], ctx["head_dim"], ctx["width"]
+        if name in ("hb_attention_prefill_tc_bf16", "hb_attention_prefill_bf16", "hb_attention_decode_bf16",
+                    "hb_attention_decode_fused_bf16", "hb_attention_simt"):
+            return n * 4.0 * pairs * H * hd, n * (2 * B * L * KV * hd * es + 2 * T * H * hd * es)
+        if name == "hb_rmsnorm":
+            return n * 4.0 * T * D, n * T * D * (4 + es)
+    return None
+
+
+def _design_point(hb, ops, torch, np, cfg, ctx, pk, prompt_len, batch, steps, warmup, windows):
+    """Prefill of one prompt and decode at `batch` for one model: tokens per second, and per launcher
+    the time of a prompt step and of an eager decode step with its distance from the roofline."""
+    rt = hb.Runtime("cuda", torch.bfloat16)
+    model = hb.random_model(cfg, 0, rt)
+    context = prompt_len + steps + warmup + 8
+    engine = hb.Engine(model, max_tokens=batch * (context + 64), max_slots=batch)
+    rng = np.random.default_rng(0)
+    V = model.spec.vocab_size
+    out = {}
+
+    def timed_step(entries, kv_len):
+        with ops.timed() as t:
+            engine.step(entries, "last")
+        rows = {}
+        c = dict(ctx, tokens=sum(len(x) for _, x in entries), seqs=len(entries), kv_len=kv_len)
+        for name, (n, ms) in t.by_kernel().items():
+            row = {"launches": n, "ms": round(ms, 4)}
+            work = _launcher_work(name, n, c)
+            if work is not None and ms > 0:
+                roof_ms = max(work[0] / (pk["bf16_tflops"] * 1e9), work[1] / (pk["hbm_gbs"] * 1e6))
+                row["of_roofline"] = round(roof_ms / ms, 4)
+            rows[name] = row
+        return rows
+
+    # prefill: one prompt
+    s = engine.alloc_slot()
+    for _ in range(max(2, warmup // 2)):
+        engine.step([(s, rng.integers(0, V, prompt_len).tolist())], "last")
+        engine.free_slot(s); s = engine.alloc_slot()
+    ids = rng.integers(0, V, prompt_len).tolist()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(); t0 = time.time()
+    e0.record(); engine.step([(s, ids)], "last"); e1.record(); torch.cuda.synchronize()
+    windows.append((t0, time.time()))
+    out["prefill_ms"] = round(e0.elapsed_time(e1), 3)
+    out["prefill_tok_s"] = round(prompt_len / e0.elapsed_time(e1) * 1e3, 1)
+    engine.free_slot(s); s = engine.alloc_slot()
+    out["prefill_by_launcher"] = timed_step([(s, ids)], prompt_len)
+    engine.free_slot(s)
+    # decode: `batch` sequences after their prompts
+    slots = [engine.alloc_slot() for _ in range(batch)]
+    for sl in slots:
+        engine.step([(sl, rng.integers(0, V, prompt_len).tolist())], "none")
+    tok = lambda: [(sl, [int(rng.integers(0, V))]) for sl in slots]  # noqa: E731
+    for _ in range(warmup):
+        engine.step(tok(), "last")
+    torch.cuda.synchronize(); t0 = time.time()
+    e0.record()
+    for _ in range(steps):
+        engine.step(tok(), "last")
+    e1.record(); torch.cuda.synchronize()
+    windows.append((t0, time.time()))
+    out["decode_ms_per_step"] = round(e0.elapsed_time(e1) / steps, 4)
+    out["decode_tok_s"] = round(batch * steps / e0.elapsed_time(e1) * 1e3, 1)
+    out["decode_kernels_per_step"] = engine.kernels_per_graph.get(batch)
+    engine.use_graphs = False
+    engine.step(tok(), "last")
+    out["decode_by_launcher"] = timed_step(tok(), prompt_len + warmup + steps + 2)
+    out["weight_bytes_per_step"] = model.weight_bytes(batch)
+    out["decode_of_hbm_roofline"] = round(out["weight_bytes_per_step"] / (pk["hbm_gbs"] * 1e6) / out["decode_ms_per_step"], 4)
+    del engine, model
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_design(args) -> int:
+    """`--design kebisun`: prefill and decode of the Kebisun design at layer sizes that resemble a real
+    model's, beside the dense decoder of equal width, depth and feed-forward width (random weights,
+    bfloat16, four layers each)."""
+    import numpy as np
+    import torch
+
+    import herbert_rs_b200 as hb
+    from herbert_rs_b200 import ops
+
+    pk = peaks()
+    sampler, windows = ClockSampler(), []
+    sampler.start()
+    result = {}
+    for size in (sorted(DESIGN_SIZES) if args.design_size == "all" else [args.design_size]):
+        kb, dense = DESIGN_SIZES[size]
+        kcfg = _kebisun_config(**kb)
+        qcfg = dict(QWEN3_8B)
+        qcfg.update(dense)
+        kctx = dict(kb, kind="kebisun")
+        qctx = dict(kind="dense", heads=dense["num_attention_heads"], kv_heads=dense["num_key_value_heads"],
+                    head_dim=dense["head_dim"], width=dense["hidden_size"])
+        result[size] = {
+            "kebisun": _design_point(hb, ops, torch, np, kcfg, kctx, pk, args.prompt_len, args.batch, args.steps, args.warmup, windows),
+            "dense": _design_point(hb, ops, torch, np, qcfg, qctx, pk, args.prompt_len, args.batch, args.steps, args.warmup, windows),
+        }
+    sampler.stop()
+    print(json.dumps({"metric": "Kebisun and the dense decoder at equal sizes: prefill and decode tokens/s", "unit": "tokens/s",
+                      "n_gpus": 1, "impl": "ours", "dtype": "bf16", "data": "synthetic", "steps": args.steps, "warmup": args.warmup,
+                      "config": {"prompt_len": args.prompt_len, "batch": args.batch, "layers": 4,
+                                 "timing": "CUDA events; every decode step reads all weights, a prompt step reads activations larger than L2 at the 2k size"},
+                      "peaks": pk, "sizes": result, "clocks": sampler.summary(windows)}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -211,6 +372,9 @@ def main() -> int:
     ap.add_argument("--pdl-graph", type=int, default=None, help="programmatic dependent launch inside recorded decode steps (0, 1, 2)")
     ap.add_argument("--workload", default=None, choices=["0.6b", "32b"],
                     help="run only this workload of the baseline and print its line")
+    ap.add_argument("--design", default=None, choices=["kebisun"],
+                    help="measure this design beside the dense decoder at equal sizes instead of the headline workload")
+    ap.add_argument("--design-size", default="all", choices=["all"] + sorted(DESIGN_SIZES))
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -218,6 +382,8 @@ def main() -> int:
         print(f"bench.py measures one GPU only (asked for {args.gpus}): this library has no multi-GPU path")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.design is not None:
+        return run_design(args)
     if args.workload is not None:
         sampler, windows = ClockSampler(), []
         sampler.start()

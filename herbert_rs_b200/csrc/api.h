@@ -136,6 +136,10 @@ int hb_headwise_gemm(int dtype, int out_dtype, const float* in, int ld_in, int i
 int hb_latent_attention(int dtype, const float* q, int ldq, float* out, int ldo, const void* cache, const float*
     sink, const int* tok_seq, const int* tok_pos, const int* seq_pages, int pages_stride, int n_tokens, int
     heads, int rank, int rot, int page_size, int window, void* stream);
+int hb_latent_attention_mma_ok(int rank, int rot);
+int hb_latent_attention_mma_bf16(const float* q, int ldq, float* out, int ldo, const void* cache, const float*
+    sink, const int* seq_start, const int* seq_pos0, const int* seq_pages, int pages_stride, int n_seqs, int
+    max_q_len, int heads, int rank, int rot, int page_size, int window, void* stream);
 
 // layernorm.cu: layer normalisation (weight, no bias), alone and with the scaled residual sum after it
 int hb_layernorm(int dtype, const float* x, const float* w, void* out, const int* rows, int n_rows, int dim,
@@ -149,6 +153,10 @@ int hb_moe_route(int dtype, const void* h, int ld, const void* w_router, int* id
 int hb_moe_experts(int dtype, const void* h, int ld, const void* up, const void* down, const int* ids, const
     float* weights, void* mid, float* y, int ldy, int n_tokens, int D, int F, int top, int act, int accumulate,
     void* stream);
+long long hb_moe_grouped_scratch_ints(int n_tokens, int E, int top);
+int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up, const void* down, const int* ids, const
+    float* weights, int* scratch, void* mid, float* part, float* y, int ldy, int n_tokens, int D, int E, int F,
+    int top, int act, int accumulate, void* stream);
 
 // sampling.cu: argmax and temperature / top-k / top-p sampling
 int hb_argmax(const float* logits, int ld, int n_rows, int vocab, int* out, void* scratch, long long

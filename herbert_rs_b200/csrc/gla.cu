@@ -46,19 +46,23 @@ extern "C" int hb_gla_decay(int dtype, const float* low, int ld, const void* w2,
 
 // ---------------------------------------------------------------------------------------------
 // The recurrence.  A block owns 32 value channels of one head of one sequence and walks that
-// sequence's tokens of the step in order; thread (x, y) keeps the state rows y, y + 4, ... of
-// column x in registers.  q, k and the decays of a token pass through shared memory.
+// sequence's tokens of the step in order; thread (x, y) keeps RPT consecutive state rows of column x
+// in registers.  q, k, v and the decays of `chunk` tokens at a time pass through shared memory, so the
+// block meets at a barrier twice per chunk, not per token; the tokens of a chunk are still taken one
+// after another, so the arithmetic is the recurrence's own, whatever the step was cut into.
 #define GLA_ROWGROUPS 4
 template <int RPT>  // rows per thread: dk <= 4 * RPT
 __global__ void __launch_bounds__(32 * GLA_ROWGROUPS)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                 float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
-                float* __restrict__ out, int ldo, int H, int dk, int dv, float qscale) {
-  extern __shared__ float sh[];  // q[dk], k[dk], a[dk], red[GLA_ROWGROUPS][32]
-  float* qs = sh;
-  float* ks = sh + dk;
-  float* as = sh + 2 * dk;
-  float* red = sh + 3 * dk;
+                float* __restrict__ out, int ldo, int H, int dk, int dv, float qscale, int chunk) {
+  constexpr int DKP = GLA_ROWGROUPS * RPT;  // padded row count; rows past dk hold zeros and stay zero
+  extern __shared__ __align__(16) float sh[];
+  float* qs = sh;                            // [chunk][DKP]
+  float* ks = qs + chunk * DKP;
+  float* as = ks + chunk * DKP;
+  float* vs = as + chunk * DKP;              // [chunk][32]
+  float* red = vs + chunk * 32;              // [chunk][GLA_ROWGROUPS][32]
   pdl_wait();
   pdl_launch();
   const int b = blockIdx.x, h = blockIdx.y, x = threadIdx.x, y = threadIdx.y;
@@ -68,39 +72,58 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
   float s[RPT];
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
-    const int r = y + GLA_ROWGROUPS * i;
+    const int r = y * RPT + i;
     s[i] = (r < dk && col < dv) ? S[(size_t)r * dv + col] : 0.0f;
   }
-  for (int t = t0; t < t1; ++t) {
-    const float* row = proj + (size_t)t * ld;
-    for (int i = tid; i < dk; i += 32 * GLA_ROWGROUPS) {
-      qs[i] = row[q_off + h * dk + i] * qscale;
-      ks[i] = row[k_off + h * dk + i];
-      as[i] = decay[(size_t)t * H * dk + h * dk + i];
+  for (int c0 = t0; c0 < t1; c0 += chunk) {
+    const int n = t1 - c0 < chunk ? t1 - c0 : chunk;
+    for (int i = tid; i < n * DKP; i += 32 * GLA_ROWGROUPS) {
+      const int tt = i / DKP, r = i - tt * DKP;
+      const float* row = proj + (size_t)(c0 + tt) * ld;
+      const bool in = r < dk;
+      qs[i] = in ? row[q_off + h * dk + r] * qscale : 0.0f;
+      ks[i] = in ? row[k_off + h * dk + r] : 0.0f;
+      as[i] = in ? decay[(size_t)(c0 + tt) * H * dk + h * dk + r] : 0.0f;
     }
-    const float v = col < dv ? row[v_off + h * dv + col] : 0.0f;
+    for (int i = tid; i < n * 32; i += 32 * GLA_ROWGROUPS) {
+      const int tt = i >> 5, c = blockIdx.z * 32 + (i & 31);
+      vs[i] = c < dv ? proj[(size_t)(c0 + tt) * ld + v_off + h * dv + c] : 0.0f;
+    }
     __syncthreads();
-    float acc = 0.0f;
+    for (int tt = 0; tt < n; ++tt) {
+      const float v = vs[tt * 32 + x];
+      const float4* a4 = reinterpret_cast<const float4*>(as + tt * DKP + y * RPT);
+      const float4* k4 = reinterpret_cast<const float4*>(ks + tt * DKP + y * RPT);
+      const float4* q4 = reinterpret_cast<const float4*>(qs + tt * DKP + y * RPT);
+      float acc = 0.0f;
 #pragma unroll
-    for (int i = 0; i < RPT; ++i) {
-      const int r = y + GLA_ROWGROUPS * i;
-      if (r < dk) {
-        s[i] = fmaf(as[r], s[i], ks[r] * v);
-        acc = fmaf(s[i], qs[r], acc);
+      for (int i = 0; i < RPT / 4; ++i) {
+        const float4 a = a4[i], k = k4[i], q = q4[i];
+        s[4 * i] = fmaf(a.x, s[4 * i], k.x * v);
+        acc = fmaf(s[4 * i], q.x, acc);
+        s[4 * i + 1] = fmaf(a.y, s[4 * i + 1], k.y * v);
+        acc = fmaf(s[4 * i + 1], q.y, acc);
+        s[4 * i + 2] = fmaf(a.z, s[4 * i + 2], k.z * v);
+        acc = fmaf(s[4 * i + 2], q.z, acc);
+        s[4 * i + 3] = fmaf(a.w, s[4 * i + 3], k.w * v);
+        acc = fmaf(s[4 * i + 3], q.w, acc);
       }
+      red[(tt * GLA_ROWGROUPS + y) * 32 + x] = acc;
     }
-    red[y * 32 + x] = acc;
     __syncthreads();
-    if (y == 0 && col < dv) {
-      float o = red[x];
+    for (int i = tid; i < n * 32; i += 32 * GLA_ROWGROUPS) {
+      const int tt = i >> 5, xx = i & 31, c = blockIdx.z * 32 + xx;
+      if (c < dv) {
+        float o = red[(tt * GLA_ROWGROUPS) * 32 + xx];
 #pragma unroll
-      for (int g = 1; g < GLA_ROWGROUPS; ++g) o += red[g * 32 + x];
-      out[(size_t)t * ldo + h * dv + col] = o;
+        for (int g = 1; g < GLA_ROWGROUPS; ++g) o += red[(tt * GLA_ROWGROUPS + g) * 32 + xx];
+        out[(size_t)(c0 + tt) * ldo + h * dv + c] = o;
+      }
     }
   }
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
-    const int r = y + GLA_ROWGROUPS * i;
+    const int r = y * RPT + i;
     if (r < dk && col < dv) S[(size_t)r * dv + col] = s[i];
   }
 }
@@ -112,11 +135,11 @@ extern "C" int hb_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
   HB_REQUIRE(dk <= 4 * 64, "gla_scan: %d key channels per head exceed the supported maximum 256", dk);
   HB_REQUIRE(heads <= 65535 && ceil_div(dv, 32) <= 65535, "gla_scan: too many heads or value channels");
   dim3 grid(n_seqs, heads, ceil_div(dv, 32)), block(32, GLA_ROWGROUPS);
-  const size_t smem = (size_t)(3 * dk + 32 * GLA_ROWGROUPS) * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;
-#define GLA_GO(RPT) \
-  hb_launch(gla_scan_kernel<RPT>, grid, block, smem, s, proj, ld, q_off, k_off, v_off, decay, state, seq_slot, seq_start, out, ldo, heads, dk, dv, qscale)
-  if (dk <= 32) GLA_GO(8); else if (dk <= 64) GLA_GO(16); else if (dk <= 128) GLA_GO(32); else GLA_GO(64);
+#define GLA_GO(RPT, CHUNK)                                                                                               \
+  hb_launch(gla_scan_kernel<RPT>, grid, block, (size_t)(CHUNK) * (3 * 4 * RPT + 32 + 32 * GLA_ROWGROUPS) * sizeof(float), s, \
+            proj, ld, q_off, k_off, v_off, decay, state, seq_slot, seq_start, out, ldo, heads, dk, dv, qscale, CHUNK)
+  if (dk <= 32) GLA_GO(8, 16); else if (dk <= 64) GLA_GO(16, 16); else if (dk <= 128) GLA_GO(32, 16); else GLA_GO(64, 8);
 #undef GLA_GO
   HB_CHECK_LAUNCH("gla_scan");
   return 0;

@@ -269,3 +269,277 @@ extern "C" int hb_latent_attention(int dtype, const float* q, int ldq, float* ou
   HB_CHECK_LAUNCH("latent_attention");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same attention on the tensor cores (bfloat16 cache, mma.sync m16n8k16), flash form.  Since all
+// heads share one cached vector per token, the rows of the score matrix are (token, head) pairs, head
+// fastest: a CTA takes 32 consecutive pairs of one sequence (with 16 heads: two tokens; a decode step:
+// all heads of the one token) against 64 keys at a time.
+//   phase 1: S = Q K^T, 32 x 64 over W = rank + rot: warp w owns rows 16 (w & 1).., keys 16 (w >> 1)..
+//   softmax: per-row maxima and sums meet in shared memory; P (bfloat16) goes to shared memory
+//   phase 2: O += P C, 32 x rank: the key tile's first `rank` columns are the values; warp w owns the
+//            16-column groups w, w + 8, ... of O for all 32 rows
+// Key tiles go global -> shared with cp.async, two buffers; a row of a tile finds its own page, so any
+// page size serves.  Masked scores never enter a maximum or a sum; the sink starts m and l.
+#include "mma_utils.cuh"
+
+#define LM_ROWS 32
+#define LM_KEYS 64
+#define LM_WARPS 8
+#define LM_THREADS (LM_WARPS * 32)
+#define LM_NEG (-1.0e30f)
+
+struct LatentMmaArgs {
+  const float* q;
+  int ldq;
+  float* out;
+  int ldo;
+  const bf16* cache;
+  const float* sink;
+  const int* seq_start;
+  const int* seq_pos0;
+  const int* seq_pages;
+  int pages_stride;
+  int H, rank, rot, page_size, window;
+};
+
+template <int NPW>  // 16-column groups of O per warp: rank <= 128 * NPW
+__global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(LatentMmaArgs a) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  pdl_wait();
+  pdl_launch();
+  const int W = a.rank + a.rot, rb = W * 2 + 16, pb = LM_KEYS * 2 + 16;
+  unsigned char* qs = smem;
+  unsigned char* kbuf = qs + LM_ROWS * rb;
+  unsigned char* ps = kbuf + 2 * LM_KEYS * rb;
+  float* smax = (float*)(ps + LM_ROWS * pb);   // [32][4]
+  float* ssum = smax + LM_ROWS * 4;            // [32][4]
+  float* mrow = ssum + LM_ROWS * 4;            // [32]
+  float* lrow = mrow + LM_ROWS;                // [32]
+  int* rowp = (int*)(lrow + LM_ROWS);          // [32] position of the row's token (-1: no row)
+  int* rowlo = rowp + LM_ROWS;                 // [32] first key the row sees
+
+  const int b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int tok0 = a.seq_start[b], nrows = (a.seq_start[b + 1] - tok0) * a.H, r0 = blockIdx.x * LM_ROWS;
+  if (r0 >= nrows) return;
+  const int pos0 = a.seq_pos0[b];
+  if (tid < LM_ROWS) {
+    const int r = r0 + tid;
+    const bool valid = r < nrows;
+    const int p = valid ? pos0 + r / a.H : -1;
+    rowp[tid] = p;
+    rowlo[tid] = (valid && a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
+    mrow[tid] = (valid && a.sink) ? a.sink[r % a.H] : LM_NEG;
+    lrow[tid] = (valid && a.sink) ? 1.0f : 0.0f;
+  }
+  for (int i = tid; i < LM_ROWS * W; i += LM_THREADS) {
+    const int rr = i / W, d = i - rr * W, r = r0 + rr;
+    const float v = r < nrows ? a.q[(size_t)(tok0 + r / a.H) * a.ldq + (size_t)(r % a.H) * W + d] : 0.0f;
+    *(bf16*)(qs + rr * rb + d * 2) = __float2bfloat16_rn(v);
+  }
+  __syncthreads();
+  const int last = (nrows - r0 < LM_ROWS ? nrows - r0 : LM_ROWS) - 1;
+  const int jmin = rowlo[0], jmax = rowp[last];
+  const int k0 = (jmin / LM_KEYS) * LM_KEYS, ntiles = (jmax - k0) / LM_KEYS + 1;
+  const int* pages = a.seq_pages + (size_t)b * a.pages_stride;
+  const int chunks = W >> 3;  // 16-byte pieces of a row
+
+  auto load_tile = [&](int it) {
+    unsigned char* dst = kbuf + (it & 1) * LM_KEYS * rb;
+    const int base = k0 + it * LM_KEYS;
+    for (int i = tid; i < LM_KEYS * chunks; i += LM_THREADS) {
+      const int kr = i / chunks, c = i - kr * chunks, j = base + kr;
+      int pi = j / a.page_size;
+      if (pi >= a.pages_stride) pi = a.pages_stride - 1;      // beyond the table: masked anyway
+      const bf16* src = a.cache + ((size_t)pages[pi] * a.page_size + (j % a.page_size)) * (size_t)W + c * 8;
+      cp_async16(dst + kr * rb + c * 16, src);
+    }
+    cp_async_commit();
+  };
+
+  float acc[2][NPW][2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < NPW; ++j)
+#pragma unroll
+      for (int k = 0; k < 2; ++k)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[i][j][k][c] = 0.0f;
+  const int npairs = a.rank >> 4;
+  const int mt = warp & 1, kg = warp >> 1;
+
+  load_tile(0);
+  for (int it = 0; it < ntiles; ++it) {
+    if (it + 1 < ntiles) {
+      load_tile(it + 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const unsigned char* kt = kbuf + (it & 1) * LM_KEYS * rb;
+    // ---- phase 1: scores of rows 16 mt.. against keys 16 kg..
+    float s[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[i][c] = 0.0f;
+    {
+      const unsigned char* qa = qs + (mt * 16 + (lane & 15)) * rb + (lane >> 4) * 16;
+      const unsigned char* kb = kt + (kg * 16 + (lane & 7) + ((lane >> 4) << 3)) * rb + ((lane >> 3) & 1) * 16;
+      for (int ks = 0; ks < (W >> 4); ++ks) {
+        unsigned a0, a1, a2, a3, b0, b1, b2, b3;
+        ldmatrix_x4(a0, a1, a2, a3, qa + ks * 32);
+        ldmatrix_x4(b0, b1, b2, b3, kb + ks * 32);
+        mma16816(s[0], a0, a1, a2, a3, b0, b1);
+        mma16816(s[1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    const int jb = k0 + it * LM_KEYS + kg * 16 + 2 * t;
+    const int ra = mt * 16 + g, rbw = ra + 8;
+    const int pa = rowp[ra], la = rowlo[ra], pbv = rowp[rbw], lb = rowlo[rbw];
+    bool ok[2][4];
+    float mxa = LM_NEG, mxb = LM_NEG;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int j = jb + nt * 8 + (c & 1);
+        const bool o = c < 2 ? (j >= la && j <= pa) : (j >= lb && j <= pbv);
+        ok[nt][c] = o;
+        if (o) {
+          if (c < 2) mxa = fmaxf(mxa, s[nt][c]); else mxb = fmaxf(mxb, s[nt][c]);
+        }
+      }
+    mxa = fmaxf(mxa, __shfl_xor_sync(0xffffffffu, mxa, 1));
+    mxa = fmaxf(mxa, __shfl_xor_sync(0xffffffffu, mxa, 2));
+    mxb = fmaxf(mxb, __shfl_xor_sync(0xffffffffu, mxb, 1));
+    mxb = fmaxf(mxb, __shfl_xor_sync(0xffffffffu, mxb, 2));
+    if (t == 0) {
+      smax[ra * 4 + kg] = mxa;
+      smax[rbw * 4 + kg] = mxb;
+    }
+    __syncthreads();
+    const float ma = fmaxf(mrow[ra], fmaxf(fmaxf(smax[ra * 4], smax[ra * 4 + 1]), fmaxf(smax[ra * 4 + 2], smax[ra * 4 + 3])));
+    const float mb = fmaxf(mrow[rbw], fmaxf(fmaxf(smax[rbw * 4], smax[rbw * 4 + 1]), fmaxf(smax[rbw * 4 + 2], smax[rbw * 4 + 3])));
+    float sa = 0.0f, sb = 0.0f;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const float p0 = ok[nt][0] ? expf(s[nt][0] - ma) : 0.0f, p1 = ok[nt][1] ? expf(s[nt][1] - ma) : 0.0f;
+      const float p2 = ok[nt][2] ? expf(s[nt][2] - mb) : 0.0f, p3 = ok[nt][3] ? expf(s[nt][3] - mb) : 0.0f;
+      // the sums take the rounded weights, the ones the product below uses
+      const __nv_bfloat162 ua = __floats2bfloat162_rn(p0, p1), ub = __floats2bfloat162_rn(p2, p3);
+      sa += __bfloat162float(ua.x) + __bfloat162float(ua.y);
+      sb += __bfloat162float(ub.x) + __bfloat162float(ub.y);
+      const int col = kg * 16 + nt * 8 + 2 * t;
+      *(__nv_bfloat162*)(ps + ra * pb + col * 2) = ua;
+      *(__nv_bfloat162*)(ps + rbw * pb + col * 2) = ub;
+    }
+    sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+    sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+    sb += __shfl_xor_sync(0xffffffffu, sb, 1);
+    sb += __shfl_xor_sync(0xffffffffu, sb, 2);
+    if (t == 0) {
+      ssum[ra * 4 + kg] = sa;
+      ssum[rbw * 4 + kg] = sb;
+    }
+    __syncthreads();
+    // ---- phase 2: O = O * corr + P C for this warp's column groups, both row tiles
+#pragma unroll
+    for (int m2 = 0; m2 < 2; ++m2) {
+      const int r1 = m2 * 16 + g, r2 = r1 + 8;
+      const float n1 = fmaxf(mrow[r1], fmaxf(fmaxf(smax[r1 * 4], smax[r1 * 4 + 1]), fmaxf(smax[r1 * 4 + 2], smax[r1 * 4 + 3])));
+      const float n2 = fmaxf(mrow[r2], fmaxf(fmaxf(smax[r2 * 4], smax[r2 * 4 + 1]), fmaxf(smax[r2 * 4 + 2], smax[r2 * 4 + 3])));
+      const float c1 = expf(mrow[r1] - n1), c2 = expf(mrow[r2] - n2);
+#pragma unroll
+      for (int j = 0; j < NPW; ++j)
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          acc[m2][j][k][0] *= c1;
+          acc[m2][j][k][1] *= c1;
+          acc[m2][j][k][2] *= c2;
+          acc[m2][j][k][3] *= c2;
+        }
+    }
+#pragma unroll
+    for (int kk = 0; kk < LM_KEYS / 16; ++kk) {
+      unsigned pa0[4], pa1[4];
+      ldmatrix_x4(pa0[0], pa0[1], pa0[2], pa0[3], ps + (lane & 15) * pb + kk * 32 + (lane >> 4) * 16);
+      ldmatrix_x4(pa1[0], pa1[1], pa1[2], pa1[3], ps + (16 + (lane & 15)) * pb + kk * 32 + (lane >> 4) * 16);
+      const unsigned char* vb = kt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * rb + (lane >> 4) * 16;
+#pragma unroll
+      for (int j = 0; j < NPW; ++j) {
+        const int pair = warp + LM_WARPS * j;
+        if (pair < npairs) {
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4_trans(b0, b1, b2, b3, vb + pair * 32);
+          mma16816(acc[0][j][0], pa0[0], pa0[1], pa0[2], pa0[3], b0, b1);
+          mma16816(acc[0][j][1], pa0[0], pa0[1], pa0[2], pa0[3], b2, b3);
+          mma16816(acc[1][j][0], pa1[0], pa1[1], pa1[2], pa1[3], b0, b1);
+          mma16816(acc[1][j][1], pa1[0], pa1[1], pa1[2], pa1[3], b2, b3);
+        }
+      }
+    }
+    __syncthreads();
+    if (tid < LM_ROWS) {
+      const float mo = mrow[tid];
+      const float mn = fmaxf(mo, fmaxf(fmaxf(smax[tid * 4], smax[tid * 4 + 1]), fmaxf(smax[tid * 4 + 2], smax[tid * 4 + 3])));
+      lrow[tid] = lrow[tid] * expf(mo - mn) + (ssum[tid * 4] + ssum[tid * 4 + 1] + ssum[tid * 4 + 2] + ssum[tid * 4 + 3]);
+      mrow[tid] = mn;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int m2 = 0; m2 < 2; ++m2)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int rr = m2 * 16 + g + half * 8, r = r0 + rr;
+      if (r >= nrows) continue;
+      const float l = lrow[rr], inv = l > 0.0f ? 1.0f / l : 0.0f;
+      float* op = a.out + (size_t)(tok0 + r / a.H) * a.ldo + (size_t)(r % a.H) * a.rank;
+#pragma unroll
+      for (int j = 0; j < NPW; ++j) {
+        const int pair = warp + LM_WARPS * j;
+        if (pair >= npairs) continue;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int col = pair * 16 + k * 8 + 2 * t;
+          op[col] = acc[m2][j][k][half * 2] * inv;
+          op[col + 1] = acc[m2][j][k][half * 2 + 1] * inv;
+        }
+      }
+    }
+}
+
+static size_t latent_mma_smem(int W) {
+  const size_t rb = (size_t)W * 2 + 16;
+  return (LM_ROWS + 2 * LM_KEYS) * rb + LM_ROWS * (LM_KEYS * 2 + 16) + LM_ROWS * 12 * sizeof(float);
+}
+
+// Whether the tensor-core kernel serves these sizes (else the any-shape kernel does).
+extern "C" int hb_latent_attention_mma_ok(int rank, int rot) {
+  return rank > 0 && rank % 16 == 0 && rot % 16 == 0 && rank <= 512 && latent_mma_smem(rank + rot) <= 220 * 1024;
+}
+
+extern "C" int hb_latent_attention_mma_bf16(const float* q, int ldq, float* out, int ldo, const void* cache, const float* sink,
+                                            const int* seq_start, const int* seq_pos0, const int* seq_pages, int pages_stride,
+                                            int n_seqs, int max_q_len, int heads, int rank, int rot, int page_size, int window,
+                                            void* stream) {
+  HB_REQUIRE(n_seqs > 0 && max_q_len > 0 && heads > 0 && page_size > 0 && window >= 0 && pages_stride > 0, "latent_attention_mma: bad sizes");
+  HB_REQUIRE(hb_latent_attention_mma_ok(rank, rot), "latent_attention_mma: rank %d and rot %d must be multiples of 16, rank at most 512", rank, rot);
+  HB_REQUIRE(n_seqs <= 65535, "latent_attention_mma: at most 65535 sequences per step");
+  const size_t smem = latent_mma_smem(rank + rot);
+  LatentMmaArgs a{q, ldq, out, ldo, (const bf16*)cache, sink, seq_start, seq_pos0, seq_pages, pages_stride, heads, rank, rot, page_size, window};
+  dim3 grid((unsigned)ceil_div_ll((long long)max_q_len * heads, LM_ROWS), n_seqs);
+  cudaStream_t s = (cudaStream_t)stream;
+#define LM_GO(NPW)                                                                                                     \
+  do {                                                                                                                 \
+    cudaFuncSetAttribute(latent_attention_mma_kernel<NPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+    hb_launch(latent_attention_mma_kernel<NPW>, grid, dim3(LM_THREADS), smem, s, a);                                   \
+  } while (0)
+  if (rank <= 128) LM_GO(1); else if (rank <= 256) LM_GO(2); else LM_GO(4);
+#undef LM_GO
+  HB_CHECK_LAUNCH("latent_attention_mma");
+  return 0;
+}

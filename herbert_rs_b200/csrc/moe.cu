@@ -13,27 +13,64 @@
 #include "common.cuh"
 
 #define MOE_WARPS 4
+#define MOE_ROUTE_WARPS 8
 
+// A warp's dot product of two rows of n numbers: 16 bytes per lane and step where the rows allow it.
+__device__ __forceinline__ float warp_dot(const float* a, const float* w, int n, int lane) {
+  float dot = 0.0f;
+  if ((n & 3) == 0 && ((((uintptr_t)a) | ((uintptr_t)w)) & 15) == 0) {
+    const float4* a4 = reinterpret_cast<const float4*>(a);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    for (int i = lane; i < (n >> 2); i += 32) {
+      const float4 x = a4[i], y = w4[i];
+      dot = fmaf(x.x, y.x, dot); dot = fmaf(x.y, y.y, dot); dot = fmaf(x.z, y.z, dot); dot = fmaf(x.w, y.w, dot);
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) dot = fmaf(a[i], w[i], dot);
+  }
+  return warp_sum(dot);
+}
+__device__ __forceinline__ float warp_dot(const bf16* a, const bf16* w, int n, int lane) {
+  float dot = 0.0f;
+  if ((n & 7) == 0 && ((((uintptr_t)a) | ((uintptr_t)w)) & 15) == 0) {
+    const uint4* a4 = reinterpret_cast<const uint4*>(a);
+    const uint4* w4 = reinterpret_cast<const uint4*>(w);
+    for (int i = lane; i < (n >> 3); i += 32) {
+      const uint4 x = a4[i], y = w4[i];
+      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
+      const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 xf = __bfloat1622float2(xp[j]), yf = __bfloat1622float2(yp[j]);
+        dot = fmaf(xf.x, yf.x, dot);
+        dot = fmaf(xf.y, yf.y, dot);
+      }
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) dot = fmaf(__bfloat162float(a[i]), __bfloat162float(w[i]), dot);
+  }
+  return warp_sum(dot);
+}
+
+// One block per token: its warps share the experts' dot products, the first warp then takes the
+// softmax and the choice.
 template <typename T>
-__global__ void __launch_bounds__(MOE_WARPS * 32)
+__global__ void __launch_bounds__(MOE_ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ h, int ld, const T* __restrict__ wr, int* __restrict__ ids, float* __restrict__ wts,
                  int n_tokens, int D, int E, int top, int renorm) {
-  extern __shared__ float sh[];  // [MOE_WARPS][E]
+  extern __shared__ float sh[];  // [E]
   pdl_wait();
   pdl_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * MOE_WARPS + warp;
-  if (t >= n_tokens) return;
-  float* s = sh + (size_t)warp * E;
+  const int t = blockIdx.x;
+  float* s = sh;
   const T* hr = h + (size_t)t * ld;
-  for (int e = 0; e < E; ++e) {
-    const T* w = wr + (size_t)e * D;
-    float dot = 0.0f;
-    for (int d = lane; d < D; d += 32) dot = fmaf(to_f32(hr[d]), to_f32(w[d]), dot);
-    dot = warp_sum(dot);
+  for (int e = warp; e < E; e += MOE_ROUTE_WARPS) {
+    const float dot = warp_dot(hr, wr + (size_t)e * D, D, lane);
     if (lane == 0) s[e] = dot;
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
   mx = warp_max(mx);
@@ -69,13 +106,13 @@ moe_route_kernel(const T* __restrict__ h, int ld, const T* __restrict__ wr, int*
 extern "C" int hb_moe_route(int dtype, const void* h, int ld, const void* w_router, int* ids, float* weights, int n_tokens,
                             int D, int E, int top, int renorm, void* stream) {
   HB_REQUIRE(n_tokens > 0 && D > 0 && E > 0 && top > 0 && top <= E, "moe_route: bad sizes (experts %d, top %d)", E, top);
-  const size_t smem = (size_t)MOE_WARPS * E * sizeof(float);
+  const size_t smem = (size_t)E * sizeof(float);
   HB_REQUIRE(smem <= 48 * 1024, "moe_route: %d experts exceed what a block keeps in shared memory", E);
-  dim3 grid(ceil_div(n_tokens, MOE_WARPS));
+  dim3 grid(n_tokens);
   if (dtype == HB_F32)
-    hb_launch(moe_route_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, (cudaStream_t)stream, (const float*)h, ld, (const float*)w_router, ids, weights, n_tokens, D, E, top, renorm);
+    hb_launch(moe_route_kernel<float>, grid, dim3(MOE_ROUTE_WARPS * 32), smem, (cudaStream_t)stream, (const float*)h, ld, (const float*)w_router, ids, weights, n_tokens, D, E, top, renorm);
   else
-    hb_launch(moe_route_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, (cudaStream_t)stream, (const bf16*)h, ld, (const bf16*)w_router, ids, weights, n_tokens, D, E, top, renorm);
+    hb_launch(moe_route_kernel<bf16>, grid, dim3(MOE_ROUTE_WARPS * 32), smem, (cudaStream_t)stream, (const bf16*)h, ld, (const bf16*)w_router, ids, weights, n_tokens, D, E, top, renorm);
   HB_CHECK_LAUNCH("moe_route");
   return 0;
 }
@@ -99,9 +136,7 @@ moe_up_kernel(const T* __restrict__ h, int ld, const T* __restrict__ up, const i
   const int e = ids[u];
   const T* w = up + ((size_t)e * F + f) * D;
   const T* hr = h + (size_t)(u / top) * ld;
-  float dot = 0.0f;
-  for (int d = lane; d < D; d += 32) dot = fmaf(to_f32(hr[d]), to_f32(w[d]), dot);
-  dot = warp_sum(dot);
+  const float dot = warp_dot(hr, w, D, lane);
   if (lane == 0) mid[(size_t)u * F + f] = from_f32<T>(moe_act(dot, act));
 }
 
@@ -120,9 +155,7 @@ moe_down_kernel(const T* __restrict__ mid, const T* __restrict__ down, const int
     const int u = t * top + r;
     const T* w = down + ((size_t)ids[u] * D + d) * F;
     const T* m = mid + (size_t)u * F;
-    float dot = 0.0f;
-    for (int f = lane; f < F; f += 32) dot = fmaf(to_f32(m[f]), to_f32(w[f]), dot);
-    acc = fmaf(wts[u], warp_sum(dot), acc);
+    acc = fmaf(wts[u], warp_dot(m, w, F, lane), acc);
   }
   if (lane == 0) {
     float* o = y + (size_t)t * ldy + d;
@@ -146,5 +179,186 @@ extern "C" int hb_moe_experts(int dtype, const void* h, int ld, const void* up, 
     hb_launch(moe_down_kernel<bf16>, g2, dim3(MOE_WARPS * 32), 0, s, (const bf16*)mid, (const bf16*)down, ids, weights, y, ldy, D, F, top, accumulate);
   }
   HB_CHECK_LAUNCH("moe_experts");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Steps of many tokens (prompts), bfloat16: the (token, choice) pairs are grouped by expert on the
+// device and each expert's pairs go through the tensor cores in tiles of 64 rows, so an expert's
+// matrices are read once per 64 pairs instead of once per pair.
+//   hb_moe_group:   counts per expert, where each expert's pairs and tiles begin, the pairs listed by expert
+//   grouped product (mma.sync m16n8k16): rows gathered through the list; first product with the
+//                   activation into mid[pair], second product into part[pair] (float)
+//   combine:        y[t] (+)= sum_r weights[t, r] * part[t * top + r]
+// Which place a pair gets inside its expert's list depends on the order in which threads arrive; a
+// pair's own numbers do not depend on its place, so the result is the same bits every time.
+#include "mma_utils.cuh"
+
+#define MG_TM 64
+#define MG_TN 64
+#define MG_TK 32
+#define MG_MAX_EXPERTS 1024
+
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict__ pair_off, int* __restrict__ tile_off,
+                 int* __restrict__ list) {
+  __shared__ int cnt[MG_MAX_EXPERTS], off[MG_MAX_EXPERTS + 1];
+  pdl_wait();
+  pdl_launch();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int u = threadIdx.x; u < n_pairs; u += blockDim.x) atomicAdd(&cnt[ids[u]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int p = 0, tl = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = p;
+      pair_off[e] = p;
+      tile_off[e] = tl;
+      p += cnt[e];
+      tl += (cnt[e] + MG_TM - 1) / MG_TM;
+    }
+    off[E] = p;
+    pair_off[E] = p;
+    tile_off[E] = tl;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int u = threadIdx.x; u < n_pairs; u += blockDim.x) {
+    const int e = ids[u];
+    list[off[e] + atomicAdd(&cnt[e], 1)] = u;
+  }
+}
+
+// C[pair, n] = sum_k A[row(pair), k] * W[e][n][k] for the pairs of tile blockIdx.x of its expert.
+// UP: row(pair) = pair / top of h, C = act(.) as bfloat16 into mid[pair]; else row(pair) = pair of mid, C float into part[pair].
+template <bool UP>
+__global__ void __launch_bounds__(128)
+moe_grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, void* __restrict__ C, int ldc,
+                        const int* __restrict__ pair_off, const int* __restrict__ tile_off, const int* __restrict__ list, int E,
+                        int N, int K, int top, int act) {
+  __shared__ __align__(16) bf16 As[2][MG_TM][MG_TK + 8];
+  __shared__ __align__(16) bf16 Ws[2][MG_TN][MG_TK + 8];
+  __shared__ int rows[MG_TM];
+  pdl_wait();
+  pdl_launch();
+  const int tile = blockIdx.x;
+  if (tile >= tile_off[E]) return;
+  int e = 0;
+  while (tile >= tile_off[e + 1]) ++e;
+  const int first = pair_off[e] + (tile - tile_off[e]) * MG_TM, end = pair_off[e + 1];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  if (tid < MG_TM) rows[tid] = first + tid < end ? list[first + tid] : -1;
+  __syncthreads();
+  const int n0 = blockIdx.y * MG_TN;
+  const bf16* We = W + (size_t)e * N * K;
+
+  auto load = [&](int buf, int k0) {
+    // 64 rows x 4 pieces of 16 bytes for A and for W: 512 pieces, 4 per thread
+    for (int i = tid; i < 2 * MG_TM * (MG_TK / 8); i += 128) {
+      const bool isw = i >= MG_TM * (MG_TK / 8);
+      const int j = isw ? i - MG_TM * (MG_TK / 8) : i;
+      const int r = j >> 2, c = (j & 3) * 8;
+      bf16* dst = isw ? &Ws[buf][r][c] : &As[buf][r][c];
+      const bf16* src = nullptr;
+      if (k0 + c < K) {
+        if (isw) {
+          if (n0 + r < N) src = We + (size_t)(n0 + r) * K + k0 + c;
+        } else if (rows[r] >= 0) {
+          src = A + (size_t)(UP ? rows[r] / top : rows[r]) * lda + k0 + c;
+        }
+      }
+      if (src) cp_async16(dst, src);
+      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
+  };
+
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[i][c] = 0.0f;
+  const int nk = (K + MG_TK - 1) / MG_TK;
+  load(0, 0);
+  for (int kb = 0; kb < nk; ++kb) {
+    if (kb + 1 < nk) {
+      load((kb + 1) & 1, (kb + 1) * MG_TK);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int buf = kb & 1;
+#pragma unroll
+    for (int ks = 0; ks < MG_TK / 16; ++ks) {
+      unsigned a0, a1, a2, a3;
+      ldmatrix_x4(a0, a1, a2, a3, &As[buf][warp * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, &Ws[buf][np * 16 + (lane & 7) + ((lane >> 4) << 3)][ks * 16 + ((lane >> 3) & 1) * 8]);
+        mma16816(acc[2 * np], a0, a1, a2, a3, b0, b1);
+        mma16816(acc[2 * np + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int pair = rows[warp * 16 + g + half * 8];
+    if (pair < 0) continue;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int n = n0 + nt * 8 + 2 * t + c;
+        if (n >= N) continue;
+        const float v = acc[nt][half * 2 + c];
+        if (UP) ((bf16*)C)[(size_t)pair * ldc + n] = __float2bfloat16_rn(moe_act(v, act));
+        else ((float*)C)[(size_t)pair * ldc + n] = v;
+      }
+  }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ part, const float* __restrict__ wts, float* __restrict__ y, int ldy,
+                                   int D, int top, int accumulate) {
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.y, d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= D) return;
+  float acc = 0.0f;
+  for (int r = 0; r < top; ++r) acc = fmaf(wts[(size_t)t * top + r], part[((size_t)t * top + r) * D + d], acc);
+  float* o = y + (size_t)t * ldy + d;
+  *o = accumulate ? *o + acc : acc;
+}
+
+extern "C" long long hb_moe_grouped_scratch_ints(int n_tokens, int E, int top) {
+  return 2LL * (E + 1) + (long long)n_tokens * top;
+}
+
+// scratch: hb_moe_grouped_scratch_ints ints; mid [T * top, F] bfloat16; part [T * top, D] floats.
+extern "C" int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up, const void* down, const int* ids,
+                                           const float* weights, int* scratch, void* mid, float* part, float* y, int ldy,
+                                           int n_tokens, int D, int E, int F, int top, int act, int accumulate,
+                                           void* stream) {
+  HB_REQUIRE(n_tokens > 0 && D > 0 && E > 0 && F > 0 && top > 0, "moe_experts_grouped: sizes must be positive");
+  HB_REQUIRE(E <= MG_MAX_EXPERTS, "moe_experts_grouped: at most %d experts", MG_MAX_EXPERTS);
+  HB_REQUIRE(D % 8 == 0 && F % 8 == 0 && ld % 8 == 0, "moe_experts_grouped: widths must be multiples of 8");
+  HB_REQUIRE(n_tokens <= 65535, "moe_experts_grouped: at most 65535 tokens per call");
+  const int n_pairs = n_tokens * top;
+  int* pair_off = scratch;
+  int* tile_off = scratch + (E + 1);
+  int* list = scratch + 2 * (E + 1);
+  cudaStream_t s = (cudaStream_t)stream;
+  hb_launch(moe_group_kernel, dim3(1), dim3(1024), 0, s, ids, n_pairs, E, pair_off, tile_off, list);
+  const int max_tiles = ceil_div(n_pairs, MG_TM) + E;
+  hb_launch(moe_grouped_gemm_kernel<true>, dim3(max_tiles, ceil_div(F, MG_TN)), dim3(128), 0, s, (const bf16*)h, ld, (const bf16*)up,
+            mid, F, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, F, D, top, act);
+  hb_launch(moe_grouped_gemm_kernel<false>, dim3(max_tiles, ceil_div(D, MG_TN)), dim3(128), 0, s, (const bf16*)mid, F,
+            (const bf16*)down, (void*)part, D, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, D, F, top, act);
+  hb_launch(moe_combine_kernel, dim3(ceil_div(D, 256), n_tokens), dim3(256), 0, s, (const float*)part, weights, y, ldy, D, top, accumulate);
+  HB_CHECK_LAUNCH("moe_experts_grouped");
   return 0;
 }

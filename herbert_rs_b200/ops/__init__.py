@@ -78,6 +78,11 @@ _SIGS = {
                          c_int, c_int, c_int, c_float, c_void_p],
     "hb_latent_attention": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_moe_experts_grouped_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_latent_attention_mma_ok": [c_int, c_int],
+    "hb_latent_attention_mma_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_gla_decay": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "hb_gla_scan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_int, c_float, c_void_p],
@@ -105,7 +110,8 @@ def _fn(name: str):
 
 
 # kernels each launcher starts (for honest launch counts)
-_KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2, "hb_argmax": 2, "hb_sample": 2, "hb_moe_experts": 2}
+_KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2, "hb_argmax": 2, "hb_sample": 2, "hb_moe_experts": 2,
+                     "hb_moe_experts_grouped_bf16": 4}
 _launches = 0
 
 
@@ -354,13 +360,20 @@ def headwise_gemm(src, src_head_stride, w, out, out_head_stride, scale=1.0, gate
          src.shape[0], H, K, N, float(scale), _stream())
 
 
-def latent_attention(q, out, cache, sink, tok_seq, tok_pos, seq_pages, heads, rank, rot, page_size, window) -> None:
+def latent_attention(q, out, cache, sink, tok_seq, tok_pos, seq_pages, heads, rank, rot, page_size, window, batch=None) -> None:
     """out[t, h, :rank] = sum_j p_j c_j over the cached rows [c_j | r_j] that the token may see, with
     scores q[t, h, :] . [c_j | r_j] (q float, already scaled) and a softmax whose denominator also holds
-    exp(sink[h]) when a sink is given."""
+    exp(sink[h]) when a sink is given.  With the step's `batch` and a bfloat16 cache whose sizes the
+    tensor-core kernel serves, that kernel runs; else the any-shape kernel."""
     _check(q, torch.float32, "q"); _check(out, torch.float32, "out")
     if sink is not None:
         _check(sink, torch.float32, "sink")
+    if batch is not None and cache.dtype == torch.bfloat16 and options.latent_attention == "mma" \
+            and _fn("hb_latent_attention_mma_ok")(int(rank), int(rot)):
+        _run("hb_latent_attention_mma_bf16", q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), cache.data_ptr(),
+             _ptr(sink), batch.seq_start.data_ptr(), batch.seq_pos0.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0),
+             batch.n_seqs, batch.max_q_len, int(heads), int(rank), int(rot), int(page_size), int(window or 0), _stream())
+        return
     _run("hb_latent_attention", dtype_code(cache.dtype), q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
          cache.data_ptr(), _ptr(sink), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0),
          q.shape[0], int(heads), int(rank), int(rot), int(page_size), int(window or 0), _stream())
@@ -398,6 +411,30 @@ def moe_route(h, w_router, ids, weights, top, renorm=False) -> None:
     _check(h, None, "h"); _check(w_router, h.dtype, "w_router"); _check(ids, torch.int32, "ids"); _check(weights, torch.float32, "weights")
     _run("hb_moe_route", dtype_code(h.dtype), h.data_ptr(), h.stride(0), w_router.data_ptr(), ids.data_ptr(), weights.data_ptr(),
          h.shape[0], h.shape[1], w_router.shape[0], int(top), 1 if renorm else 0, _stream())
+
+
+MOE_GROUPED_MIN_TOKENS = 32
+
+
+def moe_grouped_ok(h, up) -> bool:
+    """Whether a step's routed feed-forward goes through the grouped tensor-core product: bfloat16, enough
+    tokens that an expert's matrices are worth reading once per tile of pairs, widths in 16-byte pieces."""
+    E, F, D = up.shape
+    return (options.moe_grouped and h.dtype == torch.bfloat16 and MOE_GROUPED_MIN_TOKENS <= h.shape[0] <= 65535
+            and D % 8 == 0 and F % 8 == 0 and h.stride(0) % 8 == 0 and E <= 1024 and h.data_ptr() % 16 == 0)
+
+
+def moe_experts_grouped(h, up, down, ids, weights, y, act, accumulate, scratch) -> None:
+    """moe_experts for many tokens: pairs grouped by expert on the device, tiles of 64 pairs on the tensor cores."""
+    _check(h, torch.bfloat16, "h"); _check(up, torch.bfloat16, "up"); _check(down, torch.bfloat16, "down"); _check(y, torch.float32, "y")
+    T, top = ids.shape
+    E, F, D = up.shape
+    ints = scratch((2 * (E + 1) + T * top,), torch.int32)
+    mid = scratch((T * top, F), torch.bfloat16)
+    part = scratch((T * top, D), torch.float32)
+    _run("hb_moe_experts_grouped_bf16", h.data_ptr(), h.stride(0), up.data_ptr(), down.data_ptr(), ids.data_ptr(), weights.data_ptr(),
+         ints.data_ptr(), mid.data_ptr(), part.data_ptr(), y.data_ptr(), y.stride(0), T, D, E, F, top, int(act),
+         1 if accumulate else 0, _stream())
 
 
 def moe_experts(h, up, down, ids, weights, mid, y, act, accumulate=False) -> None:

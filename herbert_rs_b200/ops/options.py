@@ -32,5 +32,9 @@ class KernelOptions:
     pdl_eager: bool = True
     # The same inside recorded decode steps: 0 off, 1 every kernel, 2 only the products that load weights before they wait.
     pdl_graph: int = 0
+    # Attention over a cached latent, bfloat16: "mma" (tensor cores where the sizes allow), or "simt" (the any-shape kernel).
+    latent_attention: str = "mma"
+    # Routed feed-forward, bfloat16, steps of 32 tokens and more: pairs grouped by expert, tiles on the tensor cores.
+    moe_grouped: bool = True
     # Steps of 512 rows and more, heads of 128: per-head norm, rotation and cache write in the q/k/v product's epilogue.
     qkv_epilogue: bool = True

@@ -109,7 +109,7 @@ class LatentAttentionMixer(Mixer):
             ops.rotate_heads(q, dn + dr, dn, qa, rk + dr, rk, freq, mscale, batch.tok_pos, H, dr, scale=s.scale)
         lat = ws.take((T, H * rk), f32)
         ops.latent_attention(qa, lat, cache.k, self.sink, batch.tok_seq, batch.tok_pos, pages, H, rk, dr, cache.page_size,
-                             s.window)
+                             s.window, batch=batch)
         att = ws.take((T, H * dv), h.dtype)
         ops.headwise_gemm(lat, rk, self.w_vup, att, dv, gate=kvg[:, rk + dr:] if s.gate else None)
         ops.gemm(att, self.w_out, residual, ops.EPI_RESIDUAL if accumulate else ops.EPI_STORE_F32, scratch=ws.take)

@@ -54,8 +54,11 @@ class RoutedFeedForward(FeedForward):
         s, ws, T = self.spec, self.rt.workspace, h.shape[0]
         ids = ws.take((T, s.top_k), torch.int32)
         weights = ws.take((T, s.top_k), torch.float32)
-        mid = ws.take((T * s.top_k, s.expert_size), h.dtype)
         ops.moe_route(h, self.router, ids, weights, s.top_k, s.renormalize)
+        if ops.moe_grouped_ok(h, self.up):
+            ops.moe_experts_grouped(h, self.up, self.down, ids, weights, residual, self.act, accumulate, ws.take)
+            return
+        mid = ws.take((T * s.top_k, s.expert_size), h.dtype)
         ops.moe_experts(h, self.up, self.down, ids, weights, mid, residual, self.act, accumulate)
 
 

@@ -27,7 +27,8 @@ def ids_for(rng, cfg_or_vocab, n):
 def mixed(tmp_path_factory):
     """Both mixers, both feed-forwards, a layer without feed-forward; a window that is no multiple of anything."""
     layers = [(K.latent(window=21), K.dense()), (K.gla(), K.moe()), (K.latent(heads=2, vdim=16, window=21), None),
-              (K.gla(heads=3, dim=16, vdim=24, tau=3.0), K.dense(ff=40)), (K.latent(window=21), K.moe(experts=5, top=3, ff=16))]
+              (K.gla(heads=3, dim=16, vdim=24, tau=3.0), K.dense(ff=40)),
+              (K.latent(window=21, kv_rank=64, rot=16), K.moe(experts=5, top=3, ff=16))]     # sizes the tensor-core kernel serves
     return K.make(tmp_path_factory.mktemp("kebisun_mixed"), layers, seed=3)
 
 
@@ -92,15 +93,26 @@ def _plain_latent_scores(q, rows, p, window, sink):
     return e / (e.sum() + math.exp(sink - top)), lo
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-def test_latent_attention_sees_exactly_its_window_also_across_pages(dtype):
+class _Step:
+    """The facts of a step that the tensor-core kernel reads: one sequence of `n` queries from position `p0`."""
+
+    def __init__(self, n, p0):
+        self.n_seqs, self.max_q_len = 1, n
+        self.seq_start = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+        self.seq_pos0 = torch.tensor([p0], dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype,rank,rot,tensor_cores", [("float32", 24, 8, False), ("bfloat16", 24, 8, False),
+                                                         ("bfloat16", 32, 16, True), ("bfloat16", 144, 16, True)])
+def test_latent_attention_sees_exactly_its_window_also_across_pages(dtype, rank, rot, tensor_cores):
     """One cached row is made to stand out (its score is far above all others).  A query just inside
     the window must return that row's latent, a query one position further must not contain it: in a
     prompt's portion and for single decoded tokens, with the row at a page's last and first place, far
     back, and among the first tokens."""
     td = torch.float32 if dtype == "float32" else torch.bfloat16
-    rank, rot, H, page, window, n = 24, 8, 2, 16, 37, 200
+    H, page, window, n = 2, 16, 37, 200
     W = rank + rot
+    tol = 2e-2 if tensor_cores else 2e-5                                      # there the weights are rounded to bfloat16
     g = torch.Generator().manual_seed(5)
     rows = torch.randn(n, W, generator=g) * 0.3
     pages_of_seq = torch.randperm(16, generator=g)[:13].to(torch.int32)       # scattered physical pages
@@ -112,6 +124,8 @@ def test_latent_attention_sees_exactly_its_window_also_across_pages(dtype):
         for j in range(n):
             cache[pages_of_seq[j // page], 0, j % page] = rows_s[j].to(td)
         q1 = rows_s[star] * (12.0 / float(rows_s[star] @ rows_s[star]))       # score 12 at the star
+        if tensor_cores:
+            q1 = q1.to(torch.bfloat16).double()                               # the kernel's own rounding of the query
         for p_in in (star, star + 1, star + window - 1):                      # the star is seen ...
             for p in (p_in, star + window):                                    # ... and just not seen any more
                 if p >= n:
@@ -121,12 +135,13 @@ def test_latent_attention_sees_exactly_its_window_also_across_pages(dtype):
                 sink = torch.tensor([0.5, -1.0], device=DEV)
                 ops.latent_attention(q, out, cache.to(DEV), sink, torch.zeros(1, dtype=torch.int32, device=DEV),
                                      torch.tensor([p], dtype=torch.int32, device=DEV),
-                                     pages_of_seq.view(1, -1).to(DEV), H, rank, rot, page, window)
+                                     pages_of_seq.view(1, -1).to(DEV), H, rank, rot, page, window,
+                                     batch=_Step(1, p) if tensor_cores else None)
                 for h, qq, sk in ((0, q1, 0.5), (1, -q1, -1.0)):
                     pr, lo = _plain_latent_scores(qq, rows_s, p, window, sk)
                     ref = pr @ rows_s[lo:p + 1, :rank]
                     got = to_np(out)[0, h * rank:(h + 1) * rank]
-                    assert np.abs(got - ref.numpy()).max() < 2e-5, (star, p, h)
+                    assert np.abs(got - ref.numpy()).max() < tol, (star, p, h)
                     if h == 0:
                         weight = float(pr[star - lo]) if lo <= star <= p else 0.0
                         assert (weight > 0.9) == (p < star + window), (star, p)
@@ -134,13 +149,15 @@ def test_latent_attention_sees_exactly_its_window_also_across_pages(dtype):
     pos = torch.arange(40, 120, dtype=torch.int32)
     qs = torch.randn(len(pos), H * W, generator=g)
     out = torch.zeros(len(pos), H * rank, device=DEV)
+    if tensor_cores:
+        qs = qs.to(torch.bfloat16).float()
     ops.latent_attention(qs.to(DEV), out, cache.to(DEV), None, torch.zeros(len(pos), dtype=torch.int32, device=DEV), pos.to(DEV),
-                         pages_of_seq.view(1, -1).to(DEV), H, rank, rot, page, window)
+                         pages_of_seq.view(1, -1).to(DEV), H, rank, rot, page, window, batch=_Step(len(pos), 40) if tensor_cores else None)
     for i in (0, 7, 24, 79):
         for h in range(H):
             pr, lo = _plain_latent_scores(qs[i, h * W:(h + 1) * W].double(), rows_s, int(pos[i]), window, -math.inf)
             ref = pr @ rows_s[lo:int(pos[i]) + 1, :rank]
-            assert np.abs(to_np(out)[i, h * rank:(h + 1) * rank] - ref.numpy()).max() < 2e-5
+            assert np.abs(to_np(out)[i, h * rank:(h + 1) * rank] - ref.numpy()).max() < tol
 
 
 def test_the_recurrence_carries_its_state_between_calls_and_keeps_far_tokens():
@@ -276,7 +293,8 @@ def test_window_edges_pages_and_long_decoding(tmp_path, dtype, window):
     """Sharp attention (a few keys carry the softmax), pages of 16 positions, windows of one, a page,
     a page and one: the prompt as a whole, and 150 tokens decoded one by one, while pages the window
     left are given back and used again."""
-    layers = [(K.latent(window=window, sharp=4.0, heads=2), K.dense()), (K.latent(window=window, sharp=4.0), None)]
+    layers = [(K.latent(window=window, sharp=4.0, heads=2), K.dense()),
+              (K.latent(window=window, sharp=4.0, kv_rank=32, rot=16), None)]           # the second on the tensor cores in bfloat16
     d, pm = K.make(tmp_path / "w", layers, seed=window)
     rng = np.random.default_rng(window)
     ids = ids_for(rng, 131, 200)
