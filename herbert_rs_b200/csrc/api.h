@@ -139,7 +139,9 @@ int hb_latent_attention(int dtype, const float* q, int ldq, float* out, int ldo,
 int hb_latent_attention_mma_ok(int rank, int rot);
 int hb_latent_attention_mma_bf16(const float* q, int ldq, float* out, int ldo, const void* cache, const float*
     sink, const int* seq_start, const int* seq_pos0, const int* seq_pages, int pages_stride, int n_seqs, int
-    max_q_len, int heads, int rank, int rot, int page_size, int window, void* stream);
+    max_q_len, int heads, int rank, int rot, int page_size, int window, int nsplit, float* scratch, void*
+    stream);
+long long hb_latent_attention_mma_scratch_floats(int n_seqs, int max_q_len, int heads, int rank, int nsplit);
 
 // layernorm.cu: layer normalisation (weight, no bias), alone and with the scaled residual sum after it
 int hb_layernorm(int dtype, const float* x, const float* w, void* out, const int* rows, int n_rows, int dim,

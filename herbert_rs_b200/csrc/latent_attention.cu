@@ -18,6 +18,7 @@
 // Scores, softmax, angles and the norm of c are float on both paths.
 #include "api.h"
 #include "common.cuh"
+#include "mma_utils.cuh"
 
 // ---------------------------------------------------------------------------------------------
 // One warp per token: c = RMSNorm(kv[:rank]) * w, r = rotate(kv[rank:]), both into the cache.
@@ -106,47 +107,153 @@ extern "C" int hb_rotate_heads(const float* in, int ld_in, int in_head_stride, i
 }
 
 // ---------------------------------------------------------------------------------------------
-// A product per head:  out[t, h*out_hs + n] = scale * sum_k in[t, h*in_hs + k] * W[h][k][n]   (n < N, k < K)
-// optionally times sigmoid(gate[t, h*N + n]).  W is [H][K][N] with n innermost, so a warp reads W
-// along n.  A block takes HW_TT tokens of one head and keeps their input rows in shared memory: W is
-// read once per HW_TT tokens.
+// A product per head:  out[t, h*out_hs + n] = scale * sum_k in[t, h*in_hs + k] * W[h][n][k]   (n < N, k < K)
+// optionally times sigmoid(gate[t, h*N + n]).  W is [H][N][K] with k innermost.
+//  * few tokens: a warp per (head, n) reads its weight row once, 16 bytes per lane and step, against up to
+//    HW_TT tokens' input rows;
+//  * many tokens, bfloat16: tiles of 64 tokens x 64 outputs of one head on the tensor cores (mma.sync), the
+//    float inputs rounded to bfloat16 on their way into shared memory, as a product's inputs are.
 #define HW_TT 8
-#define HW_THREADS 128
+#define HW_WARPS 4
+__device__ __forceinline__ void hw_load8(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void hw_load8(const bf16* p, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(h2[j]);
+    v[2 * j] = f.x;
+    v[2 * j + 1] = f.y;
+  }
+}
+
 template <typename TW, typename TO>
-__global__ void __launch_bounds__(HW_THREADS)
-headwise_gemm_kernel(const float* __restrict__ in, int ld_in, int in_hs, const TW* __restrict__ w, TO* __restrict__ out,
-                     int ld_out, int out_hs, const float* __restrict__ gate, int ld_gate, int n_tokens, int K, int N,
-                     float scale) {
-  extern __shared__ float a[];  // [HW_TT][K]
+__global__ void __launch_bounds__(HW_WARPS * 32)
+headwise_dot_kernel(const float* __restrict__ in, int ld_in, int in_hs, const TW* __restrict__ w, TO* __restrict__ out,
+                    int ld_out, int out_hs, const float* __restrict__ gate, int ld_gate, int n_tokens, int K, int N,
+                    float scale, int vec) {
   pdl_wait();
   pdl_launch();
-  const int t0 = blockIdx.x * HW_TT, h = blockIdx.y;
-  for (int i = threadIdx.x; i < HW_TT * K; i += HW_THREADS) {
-    const int tt = i / K, k = i % K;
-    a[i] = (t0 + tt < n_tokens) ? in[(size_t)(t0 + tt) * ld_in + (size_t)h * in_hs + k] : 0.0f;
+  const int lane = threadIdx.x & 31, n = blockIdx.x * HW_WARPS + (threadIdx.x >> 5), h = blockIdx.y, t0 = blockIdx.z * HW_TT;
+  if (n >= N) return;
+  const TW* wr = w + ((size_t)h * N + n) * K;
+  const float* a0 = in + (size_t)t0 * ld_in + (size_t)h * in_hs;
+  const int nt = n_tokens - t0 < HW_TT ? n_tokens - t0 : HW_TT;
+  float acc[HW_TT];
+#pragma unroll
+  for (int i = 0; i < HW_TT; ++i) acc[i] = 0.0f;
+  if (vec) {
+    for (int k = lane * 8; k < K; k += 256) {
+      float wv[8], av[8];
+      hw_load8(wr + k, wv);
+#pragma unroll
+      for (int i = 0; i < HW_TT; ++i)
+        if (i < nt) {
+          hw_load8(a0 + (size_t)i * ld_in + k, av);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[i] = fmaf(av[j], wv[j], acc[i]);
+        }
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) {
+      const float wv = to_f32(wr[k]);
+#pragma unroll
+      for (int i = 0; i < HW_TT; ++i)
+        if (i < nt) acc[i] = fmaf(a0[(size_t)i * ld_in + k], wv, acc[i]);
+    }
   }
-  __syncthreads();
-  const TW* wh = w + (size_t)h * K * N;
-  for (int n = blockIdx.z * HW_THREADS + threadIdx.x; n < N; n += gridDim.z * HW_THREADS) {
-    float acc[HW_TT];
 #pragma unroll
-    for (int i = 0; i < HW_TT; ++i) acc[i] = 0.0f;
-    for (int k = 0; k < K; ++k) {
-      const float wv = to_f32(wh[(size_t)k * N + n]);
-#pragma unroll
-      for (int i = 0; i < HW_TT; ++i) acc[i] = fmaf(a[i * K + k], wv, acc[i]);
-    }
-#pragma unroll
-    for (int i = 0; i < HW_TT; ++i) {
+  for (int i = 0; i < HW_TT; ++i) {
+    const float v = warp_sum(acc[i]) * scale;
+    if (lane == 0 && i < nt) {
       const int t = t0 + i;
-      if (t >= n_tokens) break;
-      float v = acc[i] * scale;
-      if (gate) {
-        const float g = gate[(size_t)t * ld_gate + (size_t)h * N + n];
-        v *= 1.0f / (1.0f + expf(-g));
-      }
-      out[(size_t)t * ld_out + (size_t)h * out_hs + n] = from_f32<TO>(v);
+      float r = v;
+      if (gate) r *= 1.0f / (1.0f + expf(-gate[(size_t)t * ld_gate + (size_t)h * N + n]));
+      out[(size_t)t * ld_out + (size_t)h * out_hs + n] = from_f32<TO>(r);
     }
+  }
+}
+
+#define HM_TM 64
+#define HM_TN 64
+#define HM_TK 32
+template <typename TO>
+__global__ void __launch_bounds__(128)
+headwise_mma_kernel(const float* __restrict__ in, int ld_in, int in_hs, const bf16* __restrict__ w, TO* __restrict__ out,
+                    int ld_out, int out_hs, const float* __restrict__ gate, int ld_gate, int n_tokens, int K, int N,
+                    float scale) {
+  __shared__ __align__(16) bf16 As[2][HM_TM][HM_TK + 8];
+  __shared__ __align__(16) bf16 Ws[2][HM_TN][HM_TK + 8];
+  pdl_wait();
+  pdl_launch();
+  const int t0 = blockIdx.x * HM_TM, h = blockIdx.y, n0 = blockIdx.z * HM_TN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const bf16* wh = w + (size_t)h * N * K;
+  const float* ah = in + (size_t)h * in_hs;
+
+  auto load = [&](int buf, int k0) {
+    for (int i = tid; i < HM_TN * (HM_TK / 8); i += 128) {       // weights: 16-byte pieces, asynchronously
+      const int r = i >> 2, c = (i & 3) * 8;
+      if (n0 + r < N && k0 + c < K) cp_async16(&Ws[buf][r][c], wh + (size_t)(n0 + r) * K + k0 + c);
+      else *reinterpret_cast<uint4*>(&Ws[buf][r][c]) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
+    for (int i = tid; i < HM_TM * (HM_TK / 4); i += 128) {       // inputs: four floats become four bfloat16
+      const int r = i >> 3, c = (i & 7) * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t0 + r < n_tokens && k0 + c < K) v = *reinterpret_cast<const float4*>(ah + (size_t)(t0 + r) * ld_in + k0 + c);
+      *reinterpret_cast<__nv_bfloat162*>(&As[buf][r][c]) = __floats2bfloat162_rn(v.x, v.y);
+      *reinterpret_cast<__nv_bfloat162*>(&As[buf][r][c + 2]) = __floats2bfloat162_rn(v.z, v.w);
+    }
+  };
+
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[i][c] = 0.0f;
+  const int nk = (K + HM_TK - 1) / HM_TK;
+  load(0, 0);
+  for (int kb = 0; kb < nk; ++kb) {
+    if (kb + 1 < nk) {
+      load((kb + 1) & 1, (kb + 1) * HM_TK);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int buf = kb & 1;
+#pragma unroll
+    for (int ks = 0; ks < HM_TK / 16; ++ks) {
+      unsigned a0, a1, a2, a3;
+      ldmatrix_x4(a0, a1, a2, a3, &As[buf][warp * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, &Ws[buf][np * 16 + (lane & 7) + ((lane >> 4) << 3)][ks * 16 + ((lane >> 3) & 1) * 8]);
+        mma16816(acc[2 * np], a0, a1, a2, a3, b0, b1);
+        mma16816(acc[2 * np + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int tk = t0 + warp * 16 + g + half * 8;
+    if (tk >= n_tokens) continue;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int n = n0 + nt * 8 + 2 * t + c;
+        if (n >= N) continue;
+        float v = acc[nt][half * 2 + c] * scale;
+        if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)tk * ld_gate + (size_t)h * N + n]));
+        out[(size_t)tk * ld_out + (size_t)h * out_hs + n] = from_f32<TO>(v);
+      }
   }
 }
 
@@ -154,22 +261,30 @@ extern "C" int hb_headwise_gemm(int dtype, int out_dtype, const float* in, int l
                                 void* out, int ld_out, int out_head_stride, const float* gate, int ld_gate, int n_tokens,
                                 int heads, int K, int N, float scale, void* stream) {
   HB_REQUIRE(n_tokens > 0 && heads > 0 && K > 0 && N > 0, "headwise_gemm: sizes must be positive");
-  HB_REQUIRE(heads <= 65535, "headwise_gemm: at most 65535 heads");
-  const size_t smem = (size_t)HW_TT * K * sizeof(float);
-  HB_REQUIRE(smem <= 48 * 1024, "headwise_gemm: K = %d exceeds what a block keeps in shared memory", K);
-  dim3 grid(ceil_div(n_tokens, HW_TT), heads, ceil_div(N, HW_THREADS));
+  HB_REQUIRE(heads <= 65535 && ceil_div(n_tokens, HW_TT) <= 65535 && ceil_div(N, HM_TN) <= 65535, "headwise_gemm: too many heads, tokens or outputs");
   cudaStream_t s = (cudaStream_t)stream;
-#define HW_GO(TW, TO)                                                                                                           \
-  hb_launch(headwise_gemm_kernel<TW, TO>, grid, dim3(HW_THREADS), smem, s, in, ld_in, in_head_stride, (const TW*)w, (TO*)out, \
-            ld_out, out_head_stride, gate, ld_gate, n_tokens, K, N, scale)
-  if (dtype == HB_F32) {
-    HB_REQUIRE(out_dtype == HB_F32, "headwise_gemm: the 32-bit path writes floats");
-    HW_GO(float, float);
-  } else if (out_dtype == HB_F32) {
-    HW_GO(bf16, float);
-  } else {
-    HW_GO(bf16, bf16);
+  HB_REQUIRE(dtype != HB_F32 || out_dtype == HB_F32, "headwise_gemm: the 32-bit path writes floats");
+  // 16-byte loads need rows that start on 16 bytes: every stride a multiple of 8 elements (of 4 for the float inputs of the tiles)
+  const bool in4 = ld_in % 4 == 0 && in_head_stride % 4 == 0 && ((uintptr_t)in & 15) == 0;
+  const bool vec = K % 8 == 0 && ld_in % 8 == 0 && in_head_stride % 8 == 0 && ((uintptr_t)in & 31) == 0 && ((uintptr_t)w & 15) == 0;
+  if (dtype == HB_BF16 && n_tokens >= 32 && K % 8 == 0 && in4 && ((uintptr_t)w & 15) == 0) {
+    dim3 grid(ceil_div(n_tokens, HM_TM), heads, ceil_div(N, HM_TN));
+    if (out_dtype == HB_F32)
+      hb_launch(headwise_mma_kernel<float>, grid, dim3(128), 0, s, in, ld_in, in_head_stride, (const bf16*)w, (float*)out, ld_out,
+                out_head_stride, gate, ld_gate, n_tokens, K, N, scale);
+    else
+      hb_launch(headwise_mma_kernel<bf16>, grid, dim3(128), 0, s, in, ld_in, in_head_stride, (const bf16*)w, (bf16*)out, ld_out,
+                out_head_stride, gate, ld_gate, n_tokens, K, N, scale);
+    HB_CHECK_LAUNCH("headwise_gemm");
+    return 0;
   }
+  dim3 grid(ceil_div(N, HW_WARPS), heads, ceil_div(n_tokens, HW_TT));
+#define HW_GO(TW, TO)                                                                                                          \
+  hb_launch(headwise_dot_kernel<TW, TO>, grid, dim3(HW_WARPS * 32), 0, s, in, ld_in, in_head_stride, (const TW*)w, (TO*)out, ld_out, \
+            out_head_stride, gate, ld_gate, n_tokens, K, N, scale, vec ? 1 : 0)
+  if (dtype == HB_F32) HW_GO(float, float);
+  else if (out_dtype == HB_F32) HW_GO(bf16, float);
+  else HW_GO(bf16, bf16);
 #undef HW_GO
   HB_CHECK_LAUNCH("headwise_gemm");
   return 0;
@@ -281,8 +396,6 @@ extern "C" int hb_latent_attention(int dtype, const float* q, int ldq, float* ou
 //            16-column groups w, w + 8, ... of O for all 32 rows
 // Key tiles go global -> shared with cp.async, two buffers; a row of a tile finds its own page, so any
 // page size serves.  Masked scores never enter a maximum or a sum; the sink starts m and l.
-#include "mma_utils.cuh"
-
 #define LM_ROWS 32
 #define LM_KEYS 64
 #define LM_WARPS 8
@@ -301,6 +414,9 @@ struct LatentMmaArgs {
   const int* seq_pages;
   int pages_stride;
   int H, rank, rot, page_size, window;
+  int nsplit;      // key ranges per row tile; > 1: partial results go to `part` and a second kernel joins them
+  float* part;     // [seq][row tile][split][32 rows][rank + 2]: unnormalised sums, then m and l
+  int row_tiles;
 };
 
 template <int NPW>  // 16-column groups of O per warp: rank <= 128 * NPW
@@ -329,8 +445,9 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
     const int p = valid ? pos0 + r / a.H : -1;
     rowp[tid] = p;
     rowlo[tid] = (valid && a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
-    mrow[tid] = (valid && a.sink) ? a.sink[r % a.H] : LM_NEG;
-    lrow[tid] = (valid && a.sink) ? 1.0f : 0.0f;
+    const bool sunk = valid && a.sink && blockIdx.z == 0;      // the sink counts once: in the first key range
+    mrow[tid] = sunk ? a.sink[r % a.H] : LM_NEG;
+    lrow[tid] = sunk ? 1.0f : 0.0f;
   }
   for (int i = tid; i < LM_ROWS * W; i += LM_THREADS) {
     const int rr = i / W, d = i - rr * W, r = r0 + rr;
@@ -341,6 +458,8 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
   const int last = (nrows - r0 < LM_ROWS ? nrows - r0 : LM_ROWS) - 1;
   const int jmin = rowlo[0], jmax = rowp[last];
   const int k0 = (jmin / LM_KEYS) * LM_KEYS, ntiles = (jmax - k0) / LM_KEYS + 1;
+  const int per_split = (ntiles + a.nsplit - 1) / a.nsplit;
+  const int it0 = blockIdx.z * per_split, it1 = it0 + per_split < ntiles ? it0 + per_split : ntiles;
   const int* pages = a.seq_pages + (size_t)b * a.pages_stride;
   const int chunks = W >> 3;  // 16-byte pieces of a row
 
@@ -369,9 +488,9 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
   const int npairs = a.rank >> 4;
   const int mt = warp & 1, kg = warp >> 1;
 
-  load_tile(0);
-  for (int it = 0; it < ntiles; ++it) {
-    if (it + 1 < ntiles) {
+  if (it0 < it1) load_tile(it0);
+  for (int it = it0; it < it1; ++it) {
+    if (it + 1 < it1) {
       load_tile(it + 1);
       cp_async_wait<1>();
     } else {
@@ -490,14 +609,21 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
     }
   }
   __syncthreads();
+  float* pbase = a.nsplit > 1 ? a.part + ((((size_t)b * a.row_tiles + blockIdx.x) * a.nsplit + blockIdx.z) * LM_ROWS) * (size_t)(a.rank + 2)
+                              : nullptr;
+  if (pbase && tid < LM_ROWS) {
+    pbase[(size_t)tid * (a.rank + 2) + a.rank] = mrow[tid];
+    pbase[(size_t)tid * (a.rank + 2) + a.rank + 1] = lrow[tid];
+  }
 #pragma unroll
   for (int m2 = 0; m2 < 2; ++m2)
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int rr = m2 * 16 + g + half * 8, r = r0 + rr;
       if (r >= nrows) continue;
-      const float l = lrow[rr], inv = l > 0.0f ? 1.0f / l : 0.0f;
-      float* op = a.out + (size_t)(tok0 + r / a.H) * a.ldo + (size_t)(r % a.H) * a.rank;
+      const float l = lrow[rr], inv = pbase ? 1.0f : (l > 0.0f ? 1.0f / l : 0.0f);
+      float* op = pbase ? pbase + (size_t)rr * (a.rank + 2)
+                        : a.out + (size_t)(tok0 + r / a.H) * a.ldo + (size_t)(r % a.H) * a.rank;
 #pragma unroll
       for (int j = 0; j < NPW; ++j) {
         const int pair = warp + LM_WARPS * j;
@@ -512,6 +638,31 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
     }
 }
 
+// Joins the key ranges of a row: M = max m_s, out = sum_s e^{m_s - M} O_s / sum_s e^{m_s - M} l_s.  One warp per row.
+__global__ void latent_attention_join_kernel(const float* __restrict__ part, float* __restrict__ out, int ldo,
+                                             const int* __restrict__ seq_start, int H, int rank, int nsplit, int row_tiles) {
+  pdl_wait();
+  pdl_launch();
+  const int b = blockIdx.y, lane = threadIdx.x & 31;
+  const int rl = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // row within the sequence
+  const int tok0 = seq_start[b], nrows = (seq_start[b + 1] - tok0) * H;
+  if (rl >= nrows) return;
+  const int tile = rl / LM_ROWS, rr = rl % LM_ROWS;
+  const float* p0 = part + ((((size_t)b * row_tiles + tile) * nsplit) * LM_ROWS + rr) * (size_t)(rank + 2);
+  const size_t step = (size_t)LM_ROWS * (rank + 2);
+  float M = LM_NEG;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, p0[s * step + rank]);
+  float L = 0.0f;
+  for (int s = 0; s < nsplit; ++s) L += expf(p0[s * step + rank] - M) * p0[s * step + rank + 1];
+  const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+  float* op = out + (size_t)(tok0 + rl / H) * ldo + (size_t)(rl % H) * rank;
+  for (int d = lane; d < rank; d += 32) {
+    float o = 0.0f;
+    for (int s = 0; s < nsplit; ++s) o = fmaf(expf(p0[s * step + rank] - M), p0[s * step + d], o);
+    op[d] = o * inv;
+  }
+}
+
 static size_t latent_mma_smem(int W) {
   const size_t rb = (size_t)W * 2 + 16;
   return (LM_ROWS + 2 * LM_KEYS) * rb + LM_ROWS * (LM_KEYS * 2 + 16) + LM_ROWS * 12 * sizeof(float);
@@ -522,16 +673,24 @@ extern "C" int hb_latent_attention_mma_ok(int rank, int rot) {
   return rank > 0 && rank % 16 == 0 && rot % 16 == 0 && rank <= 512 && latent_mma_smem(rank + rot) <= 220 * 1024;
 }
 
+// Floats of scratch that `nsplit` key ranges need.
+extern "C" long long hb_latent_attention_mma_scratch_floats(int n_seqs, int max_q_len, int heads, int rank, int nsplit) {
+  return (long long)n_seqs * ceil_div_ll((long long)max_q_len * heads, LM_ROWS) * nsplit * LM_ROWS * (rank + 2);
+}
+
 extern "C" int hb_latent_attention_mma_bf16(const float* q, int ldq, float* out, int ldo, const void* cache, const float* sink,
                                             const int* seq_start, const int* seq_pos0, const int* seq_pages, int pages_stride,
                                             int n_seqs, int max_q_len, int heads, int rank, int rot, int page_size, int window,
-                                            void* stream) {
+                                            int nsplit, float* scratch, void* stream) {
   HB_REQUIRE(n_seqs > 0 && max_q_len > 0 && heads > 0 && page_size > 0 && window >= 0 && pages_stride > 0, "latent_attention_mma: bad sizes");
   HB_REQUIRE(hb_latent_attention_mma_ok(rank, rot), "latent_attention_mma: rank %d and rot %d must be multiples of 16, rank at most 512", rank, rot);
   HB_REQUIRE(n_seqs <= 65535, "latent_attention_mma: at most 65535 sequences per step");
+  HB_REQUIRE(nsplit >= 1 && nsplit <= 64 && (nsplit == 1 || scratch != nullptr), "latent_attention_mma: 1 to 64 key ranges, with scratch beyond one");
   const size_t smem = latent_mma_smem(rank + rot);
-  LatentMmaArgs a{q, ldq, out, ldo, (const bf16*)cache, sink, seq_start, seq_pos0, seq_pages, pages_stride, heads, rank, rot, page_size, window};
-  dim3 grid((unsigned)ceil_div_ll((long long)max_q_len * heads, LM_ROWS), n_seqs);
+  const int row_tiles = (int)ceil_div_ll((long long)max_q_len * heads, LM_ROWS);
+  LatentMmaArgs a{q, ldq, out, ldo, (const bf16*)cache, sink, seq_start, seq_pos0, seq_pages, pages_stride, heads, rank, rot, page_size, window,
+                  nsplit, scratch, row_tiles};
+  dim3 grid((unsigned)row_tiles, n_seqs, nsplit);
   cudaStream_t s = (cudaStream_t)stream;
 #define LM_GO(NPW)                                                                                                     \
   do {                                                                                                                 \
@@ -540,6 +699,9 @@ extern "C" int hb_latent_attention_mma_bf16(const float* q, int ldq, float* out,
   } while (0)
   if (rank <= 128) LM_GO(1); else if (rank <= 256) LM_GO(2); else LM_GO(4);
 #undef LM_GO
+  if (nsplit > 1)
+    hb_launch(latent_attention_join_kernel, dim3(ceil_div(max_q_len * heads, 4), n_seqs), dim3(128), 0, s, (const float*)scratch, out, ldo,
+              seq_start, heads, rank, nsplit, row_tiles);
   HB_CHECK_LAUNCH("latent_attention_mma");
   return 0;
 }

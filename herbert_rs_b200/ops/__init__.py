@@ -82,7 +82,7 @@ _SIGS = {
                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_latent_attention_mma_ok": [c_int, c_int],
     "hb_latent_attention_mma_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "hb_gla_decay": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "hb_gla_scan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_int, c_float, c_void_p],
@@ -346,33 +346,46 @@ def rotate_heads(src, src_head_stride, src_offset, out, out_head_stride, out_off
 
 
 def headwise_gemm(src, src_head_stride, w, out, out_head_stride, scale=1.0, gate=None) -> None:
-    """out[t, h*out_head_stride + n] = scale * sum_k src[t, h*src_head_stride + k] * w[h, k, n], times
-    sigmoid(gate[t, h*N + n]) if a gate (float) is given.  src float; w [H, K, N] in the compute dtype; out
+    """out[t, h*out_head_stride + n] = scale * sum_k src[t, h*src_head_stride + k] * w[h, n, k], times
+    sigmoid(gate[t, h*N + n]) if a gate (float) is given.  src float; w [H, N, K] in the compute dtype; out
     float or the compute dtype."""
     _check(src, torch.float32, "src"); _check(w, None, "w"); _check(out, None, "out")
     if not w.is_contiguous() or w.dim() != 3:
-        raise BackendError("headwise_gemm: w must be a contiguous [heads, K, N] tensor")
+        raise BackendError("headwise_gemm: w must be a contiguous [heads, N, K] tensor")
     if gate is not None:
         _check(gate, torch.float32, "gate")
-    H, K, N = w.shape
+    H, N, K = w.shape
     _run("hb_headwise_gemm", dtype_code(w.dtype), dtype_code(out.dtype), src.data_ptr(), src.stride(0), int(src_head_stride),
          w.data_ptr(), out.data_ptr(), out.stride(0), int(out_head_stride), _ptr(gate), 0 if gate is None else gate.stride(0),
          src.shape[0], H, K, N, float(scale), _stream())
 
 
-def latent_attention(q, out, cache, sink, tok_seq, tok_pos, seq_pages, heads, rank, rot, page_size, window, batch=None) -> None:
+def latent_attention(q, out, cache, sink, tok_seq, tok_pos, seq_pages, heads, rank, rot, page_size, window, batch=None,
+                     scratch=None) -> None:
     """out[t, h, :rank] = sum_j p_j c_j over the cached rows [c_j | r_j] that the token may see, with
     scores q[t, h, :] . [c_j | r_j] (q float, already scaled) and a softmax whose denominator also holds
     exp(sink[h]) when a sink is given.  With the step's `batch` and a bfloat16 cache whose sizes the
-    tensor-core kernel serves, that kernel runs; else the any-shape kernel."""
+    tensor-core kernel serves, that kernel runs; else the any-shape kernel.  A step with too few (token,
+    head) rows to fill the GPU cuts every row's keys into ranges (partial results in `scratch(shape, dtype)`,
+    joined by a second kernel), as many as the table of pages can hold tiles of, at most `latent_max_splits`."""
     _check(q, torch.float32, "q"); _check(out, torch.float32, "out")
     if sink is not None:
         _check(sink, torch.float32, "sink")
     if batch is not None and cache.dtype == torch.bfloat16 and options.latent_attention == "mma" \
             and _fn("hb_latent_attention_mma_ok")(int(rank), int(rot)):
+        ctas = batch.n_seqs * -(-batch.max_q_len * int(heads) // 32)
+        tiles = -(-min(seq_pages.shape[1] * int(page_size), int(window) + batch.max_q_len if window else 1 << 30) // 64)
+        nsplit = 1
+        if scratch is not None and 2 * ctas <= sm_count(out.device):
+            nsplit = max(1, min(sm_count(out.device) // ctas, tiles, options.latent_max_splits))
+        part = None
+        if nsplit > 1:
+            part = scratch((batch.n_seqs * -(-batch.max_q_len * int(heads) // 32) * nsplit * 32 * (int(rank) + 2),), torch.float32)
+        _KERNELS_PER_CALL["hb_latent_attention_mma_bf16"] = 2 if nsplit > 1 else 1
         _run("hb_latent_attention_mma_bf16", q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), cache.data_ptr(),
              _ptr(sink), batch.seq_start.data_ptr(), batch.seq_pos0.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0),
-             batch.n_seqs, batch.max_q_len, int(heads), int(rank), int(rot), int(page_size), int(window or 0), _stream())
+             batch.n_seqs, batch.max_q_len, int(heads), int(rank), int(rot), int(page_size), int(window or 0), nsplit,
+             _ptr(part), _stream())
         return
     _run("hb_latent_attention", dtype_code(cache.dtype), q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
          cache.data_ptr(), _ptr(sink), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0),

@@ -34,6 +34,8 @@ class KernelOptions:
     pdl_graph: int = 0
     # Attention over a cached latent, bfloat16: "mma" (tensor cores where the sizes allow), or "simt" (the any-shape kernel).
     latent_attention: str = "mma"
+    # ... whose rows' keys are cut into at most this many ranges when a step has too few rows to fill the GPU.
+    latent_max_splits: int = 16
     # Routed feed-forward, bfloat16, steps of 32 tokens and more: pairs grouped by expert, tiles on the tensor cores.
     moe_grouped: bool = True
     # Steps of 512 rows and more, heads of 128: per-head norm, rotation and cache write in the q/k/v product's epilogue.

@@ -70,8 +70,8 @@ class LatentAttentionMixer(Mixer):
         # the latent's product and the gate's read the same input: one matrix, rows [c' | r' | gate]
         self.w_kvg = torch.cat([t[n["kv_down"]]] + ([t[n["gate"]]] if s.gate else []), dim=0).contiguous()
         self.kv_norm = t[n["kv_norm"]].contiguous()
-        self.w_kup = t[n["k_up"]].view(H, self.dn, self.rk).contiguous()                      # [h][channel][latent]
-        self.w_vup = t[n["v_up"]].view(H, self.dv, self.rk).transpose(1, 2).contiguous()      # [h][latent][value]
+        self.w_kup = t[n["k_up"]].view(H, self.dn, self.rk).transpose(1, 2).contiguous()      # [h][latent][channel]: Uk_h^T
+        self.w_vup = t[n["v_up"]].view(H, self.dv, self.rk).contiguous()                      # [h][value][latent]: Uv_h
         self.sink = t[n["sink"]].contiguous() if s.sink else None
         self.w_out = t[n["out"]].contiguous()
 
@@ -109,7 +109,7 @@ class LatentAttentionMixer(Mixer):
             ops.rotate_heads(q, dn + dr, dn, qa, rk + dr, rk, freq, mscale, batch.tok_pos, H, dr, scale=s.scale)
         lat = ws.take((T, H * rk), f32)
         ops.latent_attention(qa, lat, cache.k, self.sink, batch.tok_seq, batch.tok_pos, pages, H, rk, dr, cache.page_size,
-                             s.window, batch=batch)
+                             s.window, batch=batch, scratch=ws.take)
         att = ws.take((T, H * dv), h.dtype)
         ops.headwise_gemm(lat, rk, self.w_vup, att, dv, gate=kvg[:, rk + dr:] if s.gate else None)
         ops.gemm(att, self.w_out, residual, ops.EPI_RESIDUAL if accumulate else ops.EPI_STORE_F32, scratch=ws.take)

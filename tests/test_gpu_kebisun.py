@@ -84,6 +84,25 @@ def test_rotation_with_stretched_frequencies(scaling):
     assert np.abs(got[:, :, :2]).max() == 0.0
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,K,N,stride", [(5, 3, 16, 40, 24), (70, 3, 16, 40, 24), (33, 2, 21, 10, 23), (130, 4, 72, 136, 80)])
+def test_product_per_head(dtype, T, H, K, N, stride):
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+    g = torch.Generator().manual_seed(T + K)
+    src = torch.randn(T, H * stride, generator=g)
+    w = (torch.randn(H, N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    gate = torch.randn(T, H * N, generator=g)
+    ref = torch.einsum("thk,hnk->thn", src.view(T, H, stride)[:, :, :K].double(), w.double()) * 0.7
+    out = torch.zeros(T, H * (N + 3), device=DEV)
+    ops.headwise_gemm(src.to(DEV), stride, w.to(td).to(DEV), out, N + 3, scale=0.7)
+    got = to_np(out).reshape(T, H, N + 3)
+    assert_close(got[:, :, :N], ref.numpy(), dtype, "into floats")
+    assert np.abs(got[:, :, N:]).max() == 0.0
+    out2 = torch.zeros(T, H * N, dtype=td, device=DEV)
+    ops.headwise_gemm(src.to(DEV), stride, w.to(td).to(DEV), out2, N, scale=0.7, gate=gate.to(DEV))
+    assert_close(to_np(out2).reshape(T, H, N), (ref * torch.sigmoid(gate.double()).view(T, H, N)).numpy(), dtype, "gated")
+
+
 def _plain_latent_scores(q, rows, p, window, sink):
     """Softmax over rows lo..p with a sink, sum of the first `rank` numbers: float64, one query."""
     lo = max(0, p - window + 1) if window else 0
