@@ -227,9 +227,8 @@ def _launcher_work(name, n, ctx):
     es = 2
     if ctx["kind"] == "kebisun":
         H, rk, dr, dn, dv, D = ctx["heads"], ctx["kv_rank"], ctx["rot"], ctx["dim"], ctx["vdim"], ctx["width"]
-        if name == "hb_latent_attention":
-            per = n / 1.0
-            return per * 2.0 * pairs * H * (2 * rk + dr), per * (B * L * (rk + dr) * es + T * H * (2 * rk + dr) * 4)
+        if name in ("hb_latent_attention", "hb_latent_attention_mma_bf16"):
+            return n * 2.0 * pairs * H * (2 * rk + dr), n * (B * L * (rk + dr) * es + T * H * (2 * rk + dr) * 4)
         if name == "hb_headwise_gemm":      # two per latent layer: dn -> rk and rk -> dv
             per = n / 2.0
             return per * 2.0 * T * H * rk * (dn + dv), per * (H * rk * (dn + dv) * es + T * H * (rk + dn + dr + rk + dv) * 4)
@@ -238,7 +237,7 @@ def _launcher_work(name, n, ctx):
         if name == "hb_gla_scan":
             gh, dk, gv = ctx["gla_heads"], ctx["gla_dk"], ctx["gla_dv"]
             return n * 4.0 * T * gh * dk * gv, n * (T * gh * (3 * dk + 2 * gv) * 4 + 2 * B * gh * dk * gv * 4)
-        if name == "hb_moe_experts":
+        if name in ("hb_moe_experts", "hb_moe_experts_grouped_bf16"):
             E, top, F = ctx["experts"], ctx["top"], ctx["expert_ff"]
             return n * 4.0 * T * top * F * D, n * (min(E, T * top) * 2 * F * D * es + T * D * (es + 4))
     else:

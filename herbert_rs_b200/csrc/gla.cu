@@ -47,22 +47,30 @@ extern "C" int hb_gla_decay(int dtype, const float* low, int ld, const void* w2,
 // ---------------------------------------------------------------------------------------------
 // The recurrence.  A block owns 32 value channels of one head of one sequence and walks that
 // sequence's tokens of the step in order; thread (x, y) keeps RPT consecutive state rows of column x
-// in registers.  q, k, v and the decays of `chunk` tokens at a time pass through shared memory, so the
-// block meets at a barrier twice per chunk, not per token; the tokens of a chunk are still taken one
-// after another, so the arithmetic is the recurrence's own, whatever the step was cut into.
+// in registers.  q, k, v and the decays of `chunk` tokens at a time are copied into shared memory
+// asynchronously, the next chunk while this one is worked on, so the block meets at a barrier twice
+// per chunk, not per token.  The tokens of a chunk are still taken one after another: the arithmetic
+// is the recurrence's own, whatever the step was cut into.  (q's scale multiplies the sum at the end.)
 #define GLA_ROWGROUPS 4
+#define GLA_THREADS (32 * GLA_ROWGROUPS)
+__device__ __forceinline__ void gla_copy4(float* smem, const float* gmem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void gla_copy16(float* smem, const float* gmem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem));
+}
+
 template <int RPT>  // rows per thread: dk <= 4 * RPT
-__global__ void __launch_bounds__(32 * GLA_ROWGROUPS)
+__global__ void __launch_bounds__(GLA_THREADS)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                 float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
-                float* __restrict__ out, int ldo, int H, int dk, int dv, float qscale, int chunk) {
+                float* __restrict__ out, int ldo, int H, int dk, int dv, float qscale, int chunk, int wide) {
   constexpr int DKP = GLA_ROWGROUPS * RPT;  // padded row count; rows past dk hold zeros and stay zero
   extern __shared__ __align__(16) float sh[];
-  float* qs = sh;                            // [chunk][DKP]
-  float* ks = qs + chunk * DKP;
-  float* as = ks + chunk * DKP;
-  float* vs = as + chunk * DKP;              // [chunk][32]
-  float* red = vs + chunk * 32;              // [chunk][GLA_ROWGROUPS][32]
+  const int stage_floats = chunk * (3 * DKP + 32);
+  float* red = sh + 2 * stage_floats;        // [chunk][GLA_ROWGROUPS][32]
   pdl_wait();
   pdl_launch();
   const int b = blockIdx.x, h = blockIdx.y, x = threadIdx.x, y = threadIdx.y;
@@ -75,49 +83,83 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
     const int r = y * RPT + i;
     s[i] = (r < dk && col < dv) ? S[(size_t)r * dv + col] : 0.0f;
   }
-  for (int c0 = t0; c0 < t1; c0 += chunk) {
+  for (int i = tid; i < 2 * stage_floats; i += GLA_THREADS) sh[i] = 0.0f;      // the padding stays zero from here on
+  __syncthreads();
+
+  auto stage = [&](int buf, int c0) {
+    float* qs = sh + buf * stage_floats;
+    float* ks = qs + chunk * DKP;
+    float* as = ks + chunk * DKP;
+    float* vs = as + chunk * DKP;
     const int n = t1 - c0 < chunk ? t1 - c0 : chunk;
-    for (int i = tid; i < n * DKP; i += 32 * GLA_ROWGROUPS) {
-      const int tt = i / DKP, r = i - tt * DKP;
-      const float* row = proj + (size_t)(c0 + tt) * ld;
-      const bool in = r < dk;
-      qs[i] = in ? row[q_off + h * dk + r] * qscale : 0.0f;
-      ks[i] = in ? row[k_off + h * dk + r] : 0.0f;
-      as[i] = in ? decay[(size_t)(c0 + tt) * H * dk + h * dk + r] : 0.0f;
+    if (wide) {            // every row and offset starts on 16 bytes
+      const int per = dk >> 2;
+      for (int i = tid; i < n * per; i += GLA_THREADS) {
+        const int tt = i / per, r = (i - tt * per) * 4;
+        const float* row = proj + (size_t)(c0 + tt) * ld + h * dk + r;
+        gla_copy16(qs + tt * DKP + r, row + q_off);
+        gla_copy16(ks + tt * DKP + r, row + k_off);
+        gla_copy16(as + tt * DKP + r, decay + (size_t)(c0 + tt) * H * dk + h * dk + r);
+      }
+    } else {
+      for (int i = tid; i < n * dk; i += GLA_THREADS) {
+        const int tt = i / dk, r = i - tt * dk;
+        const float* row = proj + (size_t)(c0 + tt) * ld + h * dk + r;
+        gla_copy4(qs + tt * DKP + r, row + q_off);
+        gla_copy4(ks + tt * DKP + r, row + k_off);
+        gla_copy4(as + tt * DKP + r, decay + (size_t)(c0 + tt) * H * dk + h * dk + r);
+      }
     }
-    for (int i = tid; i < n * 32; i += 32 * GLA_ROWGROUPS) {
+    for (int i = tid; i < n * 32; i += GLA_THREADS) {
       const int tt = i >> 5, c = blockIdx.z * 32 + (i & 31);
-      vs[i] = c < dv ? proj[(size_t)(c0 + tt) * ld + v_off + h * dv + c] : 0.0f;
+      if (c < dv) gla_copy4(vs + i, proj + (size_t)(c0 + tt) * ld + v_off + h * dv + c);
+    }
+    asm volatile("cp.async.commit_group;");
+  };
+
+  if (t0 < t1) stage(0, t0);
+  int buf = 0;
+  for (int c0 = t0; c0 < t1; c0 += chunk, buf ^= 1) {
+    const int n = t1 - c0 < chunk ? t1 - c0 : chunk;
+    if (c0 + chunk < t1) {
+      stage(buf ^ 1, c0 + chunk);
+      asm volatile("cp.async.wait_group 1;");
+    } else {
+      asm volatile("cp.async.wait_group 0;");
     }
     __syncthreads();
+    const float* qs = sh + buf * stage_floats;
+    const float* ks = qs + chunk * DKP;
+    const float* as = ks + chunk * DKP;
+    const float* vs = as + chunk * DKP;
     for (int tt = 0; tt < n; ++tt) {
       const float v = vs[tt * 32 + x];
       const float4* a4 = reinterpret_cast<const float4*>(as + tt * DKP + y * RPT);
       const float4* k4 = reinterpret_cast<const float4*>(ks + tt * DKP + y * RPT);
       const float4* q4 = reinterpret_cast<const float4*>(qs + tt * DKP + y * RPT);
-      float acc = 0.0f;
+      float c0a = 0.0f, c1a = 0.0f, c2a = 0.0f, c3a = 0.0f;
 #pragma unroll
       for (int i = 0; i < RPT / 4; ++i) {
         const float4 a = a4[i], k = k4[i], q = q4[i];
         s[4 * i] = fmaf(a.x, s[4 * i], k.x * v);
-        acc = fmaf(s[4 * i], q.x, acc);
+        c0a = fmaf(s[4 * i], q.x, c0a);
         s[4 * i + 1] = fmaf(a.y, s[4 * i + 1], k.y * v);
-        acc = fmaf(s[4 * i + 1], q.y, acc);
+        c1a = fmaf(s[4 * i + 1], q.y, c1a);
         s[4 * i + 2] = fmaf(a.z, s[4 * i + 2], k.z * v);
-        acc = fmaf(s[4 * i + 2], q.z, acc);
+        c2a = fmaf(s[4 * i + 2], q.z, c2a);
         s[4 * i + 3] = fmaf(a.w, s[4 * i + 3], k.w * v);
-        acc = fmaf(s[4 * i + 3], q.w, acc);
+        c3a = fmaf(s[4 * i + 3], q.w, c3a);
       }
-      red[(tt * GLA_ROWGROUPS + y) * 32 + x] = acc;
+      red[(tt * GLA_ROWGROUPS + y) * 32 + x] = (c0a + c1a) + (c2a + c3a);
     }
     __syncthreads();
-    for (int i = tid; i < n * 32; i += 32 * GLA_ROWGROUPS) {
+    for (int i = tid; i < n * 32; i += GLA_THREADS) {
       const int tt = i >> 5, xx = i & 31, c = blockIdx.z * 32 + xx;
       if (c < dv) {
         float o = red[(tt * GLA_ROWGROUPS) * 32 + xx];
 #pragma unroll
         for (int g = 1; g < GLA_ROWGROUPS; ++g) o += red[(tt * GLA_ROWGROUPS + g) * 32 + xx];
-        out[(size_t)(c0 + tt) * ldo + h * dv + c] = o;
+        out[(size_t)(c0 + tt) * ldo + h * dv + c] = o * qscale;
       }
     }
   }
@@ -136,10 +178,11 @@ extern "C" int hb_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
   HB_REQUIRE(heads <= 65535 && ceil_div(dv, 32) <= 65535, "gla_scan: too many heads or value channels");
   dim3 grid(n_seqs, heads, ceil_div(dv, 32)), block(32, GLA_ROWGROUPS);
   cudaStream_t s = (cudaStream_t)stream;
-#define GLA_GO(RPT, CHUNK)                                                                                               \
-  hb_launch(gla_scan_kernel<RPT>, grid, block, (size_t)(CHUNK) * (3 * 4 * RPT + 32 + 32 * GLA_ROWGROUPS) * sizeof(float), s, \
-            proj, ld, q_off, k_off, v_off, decay, state, seq_slot, seq_start, out, ldo, heads, dk, dv, qscale, CHUNK)
-  if (dk <= 32) GLA_GO(8, 16); else if (dk <= 64) GLA_GO(16, 16); else if (dk <= 128) GLA_GO(32, 16); else GLA_GO(64, 8);
+  const int wide = dk % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && (((uintptr_t)proj | (uintptr_t)decay) & 15) == 0;
+#define GLA_GO(RPT, CHUNK)                                                                                                    \
+  hb_launch(gla_scan_kernel<RPT>, grid, block, (size_t)(CHUNK) * (2 * (3 * 4 * RPT + 32) + 32 * GLA_ROWGROUPS) * sizeof(float), s, \
+            proj, ld, q_off, k_off, v_off, decay, state, seq_slot, seq_start, out, ldo, heads, dk, dv, qscale, CHUNK, wide)
+  if (dk <= 32) GLA_GO(8, 16); else if (dk <= 64) GLA_GO(16, 16); else if (dk <= 128) GLA_GO(32, 8); else GLA_GO(64, 4);
 #undef GLA_GO
   HB_CHECK_LAUNCH("gla_scan");
   return 0;

@@ -427,3 +427,46 @@ def test_random_weights_from_the_configuration(tmp_path):
     ids = ids_for(np.random.default_rng(1), 131, 50)
     eng = engine_for(str(tmp_path), "float32", max_tokens=256)
     assert_close(replay_whole(eng, ids), pm.logits(ids).numpy(), "float32", "random model")
+
+
+def test_command_line_trace_replay_and_prompts_in_pieces(mixed, tmp_path, capsys):
+    """The design through the library's other entry points: the command line, `bin/trace_run`, and the
+    generation loop with prompts fed in pieces and sampling on the device."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from herbert_rs_b200 import cli
+    d, pm = mixed
+    rng = np.random.default_rng(21)
+    a, b = ids_for(rng, 131, 40), ids_for(rng, 131, 7)
+    assert cli.main(["--model", d, "--prompt-ids", ",".join(map(str, a)), "--prompt-ids", ",".join(map(str, b)),
+                     "--max-tokens", "5", "--temperature", "0", "--ignore-eos", "--backend", "cuda-fp32"]) == 0
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert len(lines) == 2
+    ids = list(a)
+    for tok in map(int, lines[0].split(",")):
+        ref = pm.logits(ids)[-1].numpy()
+        assert ref.max() - ref[tok] <= 1e-4
+        ids.append(tok)
+    # trace replay: a prompt in two steps, a second request joining as a batch of its own
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[30:], "want": [9]}], "end": ["a"]},
+             {"step": 2, "entries": [{"id": "b", "tokens": b, "want": list(range(7))}], "end": ["b"]}]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "trace"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True)
+    assert r.returncode == 0 and [ln for ln in r.stdout.splitlines() if ln.startswith("done")] == ["done 0", "done 1", "done 2"]
+    ra, rb = pm.logits(a).numpy(), pm.logits(b).numpy()
+    assert_close(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, 131).astype(np.float64), ra[[0, 29]], "float32", "trace step 0")
+    assert_close(np.fromfile(out / "1.f32", dtype="<f4").reshape(1, 131).astype(np.float64), ra[[39]], "float32", "trace step 1")
+    assert_close(np.fromfile(out / "2.f32", dtype="<f4").reshape(7, 131).astype(np.float64), rb, "float32", "trace step 2")
+    # generation with prompts in pieces of 16 and sampling: the same tokens as with whole prompts
+    outs = []
+    for piece in (None, 16):
+        eng = engine_for(d, "float32", max_tokens=1024)
+        res = hb.generate(eng, [a, b], hb.GenerationOptions(max_tokens=8, ignore_eos=True, prefill_chunk_size=piece),
+                          hb.SamplingParams(temperature=0.8, top_k=20, top_p=0.95, seed=5))
+        outs.append(res.tokens)
+    assert outs[0] == outs[1]
