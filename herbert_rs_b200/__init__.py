@@ -1,4 +1,4 @@
-"""A small B200-native generation library for the dense Qwen3 decoder.
+"""A small B200-native generation library for the dense Qwen3 decoder and the Kebisun design.
 
 From a model folder (config.json + safetensors) to generated token ids on one GPU:
 
