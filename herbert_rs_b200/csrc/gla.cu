@@ -45,14 +45,14 @@ extern "C" int hb_gla_decay(int dtype, const float* low, int ld, const void* w2,
 }
 
 // ---------------------------------------------------------------------------------------------
-// The recurrence.  A block owns 32 value channels of one head of one sequence and walks that
-// sequence's tokens of the step in order; thread (x, y) keeps RPT consecutive state rows of column x
-// in registers.  q, k, v and the decays of `chunk` tokens at a time are copied into shared memory
+// The recurrence.  A block owns COLS (32, 16 or 8) value channels of one head of one sequence and walks
+// that sequence's tokens of the step in order; thread (x, y) keeps RPT consecutive state rows of column x
+// in registers, 128 / COLS groups of rows side by side (narrower blocks when a step has few sequences and
+// heads, so that one long prompt still spreads over the GPU).  q, k, v and the decays of `chunk` tokens at a time are copied into shared memory
 // asynchronously, the next chunk while this one is worked on, so the block meets at a barrier twice
 // per chunk, not per token.  The tokens of a chunk are still taken one after another: the arithmetic
 // is the recurrence's own, whatever the step was cut into.  (q's scale multiplies the sum at the end.)
-#define GLA_ROWGROUPS 4
-#define GLA_THREADS (32 * GLA_ROWGROUPS)
+#define GLA_THREADS 128
 __device__ __forceinline__ void gla_copy4(float* smem, const float* gmem) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem));
@@ -62,19 +62,20 @@ __device__ __forceinline__ void gla_copy16(float* smem, const float* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem));
 }
 
-template <int RPT>  // rows per thread: dk <= 4 * RPT
+template <int RPT, int COLS>  // rows per thread: dk <= (128 / COLS) * RPT
 __global__ void __launch_bounds__(GLA_THREADS)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                 float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                 float* __restrict__ out, int ldo, int H, int dk, int dv, float qscale, int chunk, int wide) {
+  constexpr int GLA_ROWGROUPS = GLA_THREADS / COLS;
   constexpr int DKP = GLA_ROWGROUPS * RPT;  // padded row count; rows past dk hold zeros and stay zero
   extern __shared__ __align__(16) float sh[];
-  const int stage_floats = chunk * (3 * DKP + 32);
-  float* red = sh + 2 * stage_floats;        // [chunk][GLA_ROWGROUPS][32]
+  const int stage_floats = chunk * (3 * DKP + COLS);
+  float* red = sh + 2 * stage_floats;        // [chunk][GLA_ROWGROUPS][COLS]
   pdl_wait();
   pdl_launch();
   const int b = blockIdx.x, h = blockIdx.y, x = threadIdx.x, y = threadIdx.y;
-  const int col = blockIdx.z * 32 + x, tid = y * 32 + x;
+  const int col = blockIdx.z * COLS + x, tid = y * COLS + x;
   const int t0 = seq_start[b], t1 = seq_start[b + 1];
   float* S = state + (((size_t)seq_slot[b] * H + h) * dk) * (size_t)dv;
   float s[RPT];
@@ -110,8 +111,8 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
         gla_copy4(as + tt * DKP + r, decay + (size_t)(c0 + tt) * H * dk + h * dk + r);
       }
     }
-    for (int i = tid; i < n * 32; i += GLA_THREADS) {
-      const int tt = i >> 5, c = blockIdx.z * 32 + (i & 31);
+    for (int i = tid; i < n * COLS; i += GLA_THREADS) {
+      const int tt = i / COLS, c = blockIdx.z * COLS + (i % COLS);
       if (c < dv) gla_copy4(vs + i, proj + (size_t)(c0 + tt) * ld + v_off + h * dv + c);
     }
     asm volatile("cp.async.commit_group;");
@@ -133,7 +134,7 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
     const float* as = ks + chunk * DKP;
     const float* vs = as + chunk * DKP;
     for (int tt = 0; tt < n; ++tt) {
-      const float v = vs[tt * 32 + x];
+      const float v = vs[tt * COLS + x];
       const float4* a4 = reinterpret_cast<const float4*>(as + tt * DKP + y * RPT);
       const float4* k4 = reinterpret_cast<const float4*>(ks + tt * DKP + y * RPT);
       const float4* q4 = reinterpret_cast<const float4*>(qs + tt * DKP + y * RPT);
@@ -150,15 +151,15 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
         s[4 * i + 3] = fmaf(a.w, s[4 * i + 3], k.w * v);
         c3a = fmaf(s[4 * i + 3], q.w, c3a);
       }
-      red[(tt * GLA_ROWGROUPS + y) * 32 + x] = (c0a + c1a) + (c2a + c3a);
+      red[(tt * GLA_ROWGROUPS + y) * COLS + x] = (c0a + c1a) + (c2a + c3a);
     }
     __syncthreads();
-    for (int i = tid; i < n * 32; i += GLA_THREADS) {
-      const int tt = i >> 5, xx = i & 31, c = blockIdx.z * 32 + xx;
+    for (int i = tid; i < n * COLS; i += GLA_THREADS) {
+      const int tt = i / COLS, xx = i % COLS, c = blockIdx.z * COLS + xx;
       if (c < dv) {
-        float o = red[(tt * GLA_ROWGROUPS) * 32 + xx];
+        float o = red[(tt * GLA_ROWGROUPS) * COLS + xx];
 #pragma unroll
-        for (int g = 1; g < GLA_ROWGROUPS; ++g) o += red[(tt * GLA_ROWGROUPS + g) * 32 + xx];
+        for (int g = 1; g < GLA_ROWGROUPS; ++g) o += red[(tt * GLA_ROWGROUPS + g) * COLS + xx];
         out[(size_t)(c0 + tt) * ldo + h * dv + c] = o * qscale;
       }
     }
@@ -175,39 +176,59 @@ extern "C" int hb_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
                            int dv, float qscale, void* stream) {
   HB_REQUIRE(n_seqs > 0 && heads > 0 && dk > 0 && dv > 0, "gla_scan: sizes must be positive");
   HB_REQUIRE(dk <= 4 * 64, "gla_scan: %d key channels per head exceed the supported maximum 256", dk);
-  HB_REQUIRE(heads <= 65535 && ceil_div(dv, 32) <= 65535, "gla_scan: too many heads or value channels");
-  dim3 grid(n_seqs, heads, ceil_div(dv, 32)), block(32, GLA_ROWGROUPS);
+  HB_REQUIRE(heads <= 65535 && ceil_div(dv, 8) <= 65535, "gla_scan: too many heads or value channels");
   cudaStream_t s = (cudaStream_t)stream;
   const int wide = dk % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && (((uintptr_t)proj | (uintptr_t)decay) & 15) == 0;
-#define GLA_GO(RPT, CHUNK)                                                                                                    \
-  hb_launch(gla_scan_kernel<RPT>, grid, block, (size_t)(CHUNK) * (2 * (3 * 4 * RPT + 32) + 32 * GLA_ROWGROUPS) * sizeof(float), s, \
-            proj, ld, q_off, k_off, v_off, decay, state, seq_slot, seq_start, out, ldo, heads, dk, dv, qscale, CHUNK, wide)
-  if (dk <= 32) GLA_GO(8, 16); else if (dk <= 64) GLA_GO(16, 16); else if (dk <= 128) GLA_GO(32, 8); else GLA_GO(64, 4);
+  // the widest blocks that still give every SM one (a long prompt alone: narrower blocks, more of them)
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int cols = 32;
+  while (cols > 8 && (long long)n_seqs * heads * ceil_div(dv, cols) < sms) cols >>= 1;
+  const int groups = GLA_THREADS / cols;
+  int rpt = ceil_div(ceil_div(dk, groups), 4) * 4;                 // rows per thread, whole float4s
+  rpt = rpt <= 4 ? 4 : rpt <= 8 ? 8 : rpt <= 16 ? 16 : rpt <= 32 ? 32 : 64;
+  const int chunk = rpt * groups <= 64 ? 16 : rpt * groups <= 128 ? 8 : 4;
+  dim3 grid(n_seqs, heads, ceil_div(dv, cols)), block(cols, groups);
+  const size_t smem = (size_t)chunk * (2 * (3 * groups * rpt + cols) + GLA_THREADS) * sizeof(float);
+#define GLA_GO(RPT, COLS)                                                                                                   \
+  hb_launch(gla_scan_kernel<RPT, COLS>, grid, block, smem, s, proj, ld, q_off, k_off, v_off, decay, state, seq_slot, seq_start, \
+            out, ldo, heads, dk, dv, qscale, chunk, wide)
+#define GLA_COLS(RPT)                                       \
+  do {                                                      \
+    if (cols == 32) GLA_GO(RPT, 32);                        \
+    else if (cols == 16) GLA_GO(RPT, 16);                   \
+    else GLA_GO(RPT, 8);                                    \
+  } while (0)
+  if (rpt == 4) GLA_COLS(4); else if (rpt == 8) GLA_COLS(8); else if (rpt == 16) GLA_COLS(16); else if (rpt == 32) GLA_COLS(32);
+  else {
+    HB_REQUIRE(cols == 32, "gla_scan: internal: 64 rows per thread only with 32 columns");
+    GLA_GO(64, 32);
+  }
+#undef GLA_COLS
 #undef GLA_GO
   HB_CHECK_LAUNCH("gla_scan");
   return 0;
 }
 
 // ---------------------------------------------------------------------------------------------
-// y[t, h, :] = o / sqrt(mean(o^2) + eps) * w * silu(g[t, h, :]).  One warp per (token, head).
+// y[t, h, :] = o / sqrt(mean(o^2) + eps) * w * silu(g[t, h, :]).  One CTA of 128 threads per (token, head).
 template <typename T>
-__global__ void gla_output_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ w, float eps,
-                                  const float* __restrict__ gate, int ldg, T* __restrict__ y, int ldy, int n_tokens, int H,
-                                  int dv) {
+__global__ void __launch_bounds__(128)
+gla_output_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ w, float eps, const float* __restrict__ gate,
+                  int ldg, T* __restrict__ y, int ldy, int n_tokens, int H, int dv) {
+  __shared__ float red[32];
   pdl_wait();
   pdl_launch();
-  const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (unit >= (long long)n_tokens * H) return;
-  const int t = (int)(unit / H), h = (int)(unit % H);
+  const int t = blockIdx.x / H, h = blockIdx.x % H;
   const float* orow = o + (size_t)t * ldo + (size_t)h * dv;
   float ss = 0.0f;
-  for (int d = lane; d < dv; d += 32) ss += orow[d] * orow[d];
-  ss = warp_sum(ss);
+  for (int d = threadIdx.x; d < dv; d += blockDim.x) ss += orow[d] * orow[d];
+  ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
   const float* g = gate + (size_t)t * ldg + (size_t)h * dv;
   T* yr = y + (size_t)t * ldy + (size_t)h * dv;
-  for (int d = lane; d < dv; d += 32) {
+  for (int d = threadIdx.x; d < dv; d += blockDim.x) {
     const float gv = g[d];
     yr[d] = from_f32<T>(((orow[d] * inv) * w[d]) * (gv / (1.0f + expf(-gv))));
   }
@@ -216,12 +237,13 @@ __global__ void gla_output_kernel(const float* __restrict__ o, int ldo, const fl
 extern "C" int hb_gla_output(int dtype, const float* o, int ldo, const float* w, float eps, const float* gate, int ldg,
                              void* y, int ldy, int n_tokens, int heads, int dv, void* stream) {
   HB_REQUIRE(n_tokens > 0 && heads > 0 && dv > 0, "gla_output: sizes must be positive");
-  const long long blocks = ceil_div_ll((long long)n_tokens * heads, 4);
+  const long long blocks = (long long)n_tokens * heads;
   HB_REQUIRE(blocks < 2147483647LL, "gla_output: too many (token, head) pairs");
+  const int threads = dv >= 128 ? 128 : (dv >= 64 ? 64 : 32);
   if (dtype == HB_F32)
-    hb_launch(gla_output_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, (cudaStream_t)stream, o, ldo, w, eps, gate, ldg, (float*)y, ldy, n_tokens, heads, dv);
+    hb_launch(gla_output_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream, o, ldo, w, eps, gate, ldg, (float*)y, ldy, n_tokens, heads, dv);
   else
-    hb_launch(gla_output_kernel<bf16>, dim3((unsigned)blocks), dim3(128), 0, (cudaStream_t)stream, o, ldo, w, eps, gate, ldg, (bf16*)y, ldy, n_tokens, heads, dv);
+    hb_launch(gla_output_kernel<bf16>, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream, o, ldo, w, eps, gate, ldg, (bf16*)y, ldy, n_tokens, heads, dv);
   HB_CHECK_LAUNCH("gla_output");
   return 0;
 }

@@ -449,10 +449,11 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
     mrow[tid] = sunk ? a.sink[r % a.H] : LM_NEG;
     lrow[tid] = sunk ? 1.0f : 0.0f;
   }
-  for (int i = tid; i < LM_ROWS * W; i += LM_THREADS) {
-    const int rr = i / W, d = i - rr * W, r = r0 + rr;
-    const float v = r < nrows ? a.q[(size_t)(tok0 + r / a.H) * a.ldq + (size_t)(r % a.H) * W + d] : 0.0f;
-    *(bf16*)(qs + rr * rb + d * 2) = __float2bfloat16_rn(v);
+  for (int rr = warp; rr < LM_ROWS; rr += LM_WARPS) {      // a row per warp and turn: no division per element
+    const int r = r0 + rr;
+    const float* src = r < nrows ? a.q + (size_t)(tok0 + r / a.H) * a.ldq + (size_t)(r % a.H) * W : nullptr;
+    bf16* dst = (bf16*)(qs + rr * rb);
+    for (int d = lane; d < W; d += 32) dst[d] = __float2bfloat16_rn(src ? src[d] : 0.0f);
   }
   __syncthreads();
   const int last = (nrows - r0 < LM_ROWS ? nrows - r0 : LM_ROWS) - 1;
@@ -463,15 +464,22 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
   const int* pages = a.seq_pages + (size_t)b * a.pages_stride;
   const int chunks = W >> 3;  // 16-byte pieces of a row
 
+  const bool whole_pages = a.page_size % LM_KEYS == 0;     // then a tile of keys lies inside one page
   auto load_tile = [&](int it) {
     unsigned char* dst = kbuf + (it & 1) * LM_KEYS * rb;
     const int base = k0 + it * LM_KEYS;
-    for (int i = tid; i < LM_KEYS * chunks; i += LM_THREADS) {
-      const int kr = i / chunks, c = i - kr * chunks, j = base + kr;
-      int pi = j / a.page_size;
-      if (pi >= a.pages_stride) pi = a.pages_stride - 1;      // beyond the table: masked anyway
-      const bf16* src = a.cache + ((size_t)pages[pi] * a.page_size + (j % a.page_size)) * (size_t)W + c * 8;
-      cp_async16(dst + kr * rb + c * 16, src);
+    int pi0 = base / a.page_size;
+    if (pi0 >= a.pages_stride) pi0 = a.pages_stride - 1;    // beyond the table: masked anyway
+    const bf16* tile0 = a.cache + ((size_t)pages[pi0] * a.page_size + (base % a.page_size)) * (size_t)W;
+    for (int kr = warp; kr < LM_KEYS; kr += LM_WARPS) {     // a key row per warp and turn
+      const bf16* src = tile0 + (size_t)kr * W;
+      if (!whole_pages) {
+        const int j = base + kr;
+        int pi = j / a.page_size;
+        if (pi >= a.pages_stride) pi = a.pages_stride - 1;
+        src = a.cache + ((size_t)pages[pi] * a.page_size + (j % a.page_size)) * (size_t)W;
+      }
+      for (int c = lane; c < chunks; c += 32) cp_async16(dst + kr * rb + c * 16, src + c * 8);
     }
     cp_async_commit();
   };
@@ -499,22 +507,41 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
     __syncthreads();
     const unsigned char* kt = kbuf + (it & 1) * LM_KEYS * rb;
     // ---- phase 1: scores of rows 16 mt.. against keys 16 kg..
-    float s[2][4];
+    // four sets of partial sums over k, so that four instructions per score tile are in flight, not one after the other
+    float s[2][4], sp[4][2][4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int u = 0; u < 4; ++u)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) s[i][c] = 0.0f;
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sp[u][i][c] = 0.0f;
     {
       const unsigned char* qa = qs + (mt * 16 + (lane & 15)) * rb + (lane >> 4) * 16;
       const unsigned char* kb = kt + (kg * 16 + (lane & 7) + ((lane >> 4) << 3)) * rb + ((lane >> 3) & 1) * 16;
-      for (int ks = 0; ks < (W >> 4); ++ks) {
+      const int nks = W >> 4;
+      int ks = 0;
+      for (; ks + 4 <= nks; ks += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          unsigned a0, a1, a2, a3, b0, b1, b2, b3;
+          ldmatrix_x4(a0, a1, a2, a3, qa + (ks + u) * 32);
+          ldmatrix_x4(b0, b1, b2, b3, kb + (ks + u) * 32);
+          mma16816(sp[u][0], a0, a1, a2, a3, b0, b1);
+          mma16816(sp[u][1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+      for (; ks < nks; ++ks) {
         unsigned a0, a1, a2, a3, b0, b1, b2, b3;
         ldmatrix_x4(a0, a1, a2, a3, qa + ks * 32);
         ldmatrix_x4(b0, b1, b2, b3, kb + ks * 32);
-        mma16816(s[0], a0, a1, a2, a3, b0, b1);
-        mma16816(s[1], a0, a1, a2, a3, b2, b3);
+        mma16816(sp[0][0], a0, a1, a2, a3, b0, b1);
+        mma16816(sp[0][1], a0, a1, a2, a3, b2, b3);
       }
     }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[i][c] = (sp[0][i][c] + sp[1][i][c]) + (sp[2][i][c] + sp[3][i][c]);
     const int jb = k0 + it * LM_KEYS + kg * 16 + 2 * t;
     const int ra = mt * 16 + g, rbw = ra + 8;
     const int pa = rowp[ra], la = rowlo[ra], pbv = rowp[rbw], lb = rowlo[rbw];
@@ -638,28 +665,38 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
     }
 }
 
-// Joins the key ranges of a row: M = max m_s, out = sum_s e^{m_s - M} O_s / sum_s e^{m_s - M} l_s.  One warp per row.
-__global__ void latent_attention_join_kernel(const float* __restrict__ part, float* __restrict__ out, int ldo,
-                                             const int* __restrict__ seq_start, int H, int rank, int nsplit, int row_tiles) {
+// Joins the key ranges of a row: M = max m_s, out = sum_s e^{m_s - M} O_s / sum_s e^{m_s - M} l_s.  One CTA per
+// row; its threads share the ranges' factors and take the row's columns side by side.
+#define LJ_THREADS 128
+__global__ void __launch_bounds__(LJ_THREADS)
+latent_attention_join_kernel(const float* __restrict__ part, float* __restrict__ out, int ldo, const int* __restrict__ seq_start,
+                             int H, int rank, int nsplit, int row_tiles) {
+  __shared__ float f[64];
   pdl_wait();
   pdl_launch();
-  const int b = blockIdx.y, lane = threadIdx.x & 31;
-  const int rl = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // row within the sequence
+  const int b = blockIdx.y, rl = blockIdx.x;      // row within the sequence
   const int tok0 = seq_start[b], nrows = (seq_start[b + 1] - tok0) * H;
   if (rl >= nrows) return;
   const int tile = rl / LM_ROWS, rr = rl % LM_ROWS;
   const float* p0 = part + ((((size_t)b * row_tiles + tile) * nsplit) * LM_ROWS + rr) * (size_t)(rank + 2);
   const size_t step = (size_t)LM_ROWS * (rank + 2);
-  float M = LM_NEG;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, p0[s * step + rank]);
-  float L = 0.0f;
-  for (int s = 0; s < nsplit; ++s) L += expf(p0[s * step + rank] - M) * p0[s * step + rank + 1];
-  const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float m0 = lane < nsplit ? p0[lane * step + rank] : LM_NEG, m1 = lane + 32 < nsplit ? p0[(lane + 32) * step + rank] : LM_NEG;
+    const float M = warp_max(fmaxf(m0, m1));
+    const float e0 = lane < nsplit ? expf(m0 - M) : 0.0f, e1 = lane + 32 < nsplit ? expf(m1 - M) : 0.0f;
+    float L = (lane < nsplit ? e0 * p0[lane * step + rank + 1] : 0.0f) + (lane + 32 < nsplit ? e1 * p0[(lane + 32) * step + rank + 1] : 0.0f);
+    L = warp_sum(L);
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    f[lane] = e0 * inv;
+    f[lane + 32] = e1 * inv;
+  }
+  __syncthreads();
   float* op = out + (size_t)(tok0 + rl / H) * ldo + (size_t)(rl % H) * rank;
-  for (int d = lane; d < rank; d += 32) {
+  for (int d = threadIdx.x; d < rank; d += LJ_THREADS) {
     float o = 0.0f;
-    for (int s = 0; s < nsplit; ++s) o = fmaf(expf(p0[s * step + rank] - M), p0[s * step + d], o);
-    op[d] = o * inv;
+    for (int s = 0; s < nsplit; ++s) o = fmaf(f[s], p0[s * step + d], o);
+    op[d] = o;
   }
 }
 
@@ -700,7 +737,7 @@ extern "C" int hb_latent_attention_mma_bf16(const float* q, int ldq, float* out,
   if (rank <= 128) LM_GO(1); else if (rank <= 256) LM_GO(2); else LM_GO(4);
 #undef LM_GO
   if (nsplit > 1)
-    hb_launch(latent_attention_join_kernel, dim3(ceil_div(max_q_len * heads, 4), n_seqs), dim3(128), 0, s, (const float*)scratch, out, ldo,
+    hb_launch(latent_attention_join_kernel, dim3(max_q_len * heads, n_seqs), dim3(LJ_THREADS), 0, s, (const float*)scratch, out, ldo,
               seq_start, heads, rank, nsplit, row_tiles);
   HB_CHECK_LAUNCH("latent_attention_mma");
   return 0;

@@ -196,7 +196,7 @@ extern "C" int hb_moe_experts(int dtype, const void* h, int ld, const void* up, 
 
 #define MG_TM 64
 #define MG_TN 64
-#define MG_TK 32
+#define MG_TK 64
 #define MG_MAX_EXPERTS 1024
 
 __global__ void __launch_bounds__(1024)
@@ -255,11 +255,11 @@ moe_grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restr
   const bf16* We = W + (size_t)e * N * K;
 
   auto load = [&](int buf, int k0) {
-    // 64 rows x 4 pieces of 16 bytes for A and for W: 512 pieces, 4 per thread
+    // 64 rows x MG_TK / 8 pieces of 16 bytes for A and as many for W
     for (int i = tid; i < 2 * MG_TM * (MG_TK / 8); i += 128) {
       const bool isw = i >= MG_TM * (MG_TK / 8);
       const int j = isw ? i - MG_TM * (MG_TK / 8) : i;
-      const int r = j >> 2, c = (j & 3) * 8;
+      const int r = j / (MG_TK / 8), c = (j % (MG_TK / 8)) * 8;
       bf16* dst = isw ? &Ws[buf][r][c] : &As[buf][r][c];
       const bf16* src = nullptr;
       if (k0 + c < K) {
