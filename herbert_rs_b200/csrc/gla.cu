@@ -188,12 +188,15 @@ extern "C" int hb_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
   const int groups = GLA_THREADS / cols;
   int rpt = ceil_div(ceil_div(dk, groups), 4) * 4;                 // rows per thread, whole float4s
   rpt = rpt <= 4 ? 4 : rpt <= 8 ? 8 : rpt <= 16 ? 16 : rpt <= 32 ? 32 : 64;
-  const int chunk = rpt * groups <= 64 ? 16 : rpt * groups <= 128 ? 8 : 4;
+  const int chunk = 16;     // tokens per stage: enough work per stage to cover the next stage's way from memory
   dim3 grid(n_seqs, heads, ceil_div(dv, cols)), block(cols, groups);
   const size_t smem = (size_t)chunk * (2 * (3 * groups * rpt + cols) + GLA_THREADS) * sizeof(float);
-#define GLA_GO(RPT, COLS)                                                                                                   \
-  hb_launch(gla_scan_kernel<RPT, COLS>, grid, block, smem, s, proj, ld, q_off, k_off, v_off, decay, state, seq_slot, seq_start, \
-            out, ldo, heads, dk, dv, qscale, chunk, wide)
+#define GLA_GO(RPT, COLS)                                                                                                       \
+  do {                                                                                                                          \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(gla_scan_kernel<RPT, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    hb_launch(gla_scan_kernel<RPT, COLS>, grid, block, smem, s, proj, ld, q_off, k_off, v_off, decay, state, seq_slot, seq_start, \
+              out, ldo, heads, dk, dv, qscale, chunk, wide);                                                                    \
+  } while (0)
 #define GLA_COLS(RPT)                                       \
   do {                                                      \
     if (cols == 32) GLA_GO(RPT, 32);                        \

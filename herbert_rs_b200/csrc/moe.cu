@@ -184,8 +184,8 @@ extern "C" int hb_moe_experts(int dtype, const void* h, int ld, const void* up, 
 
 // ---------------------------------------------------------------------------------------------
 // Steps of many tokens (prompts), bfloat16: the (token, choice) pairs are grouped by expert on the
-// device and each expert's pairs go through the tensor cores in tiles of 64 rows, so an expert's
-// matrices are read once per 64 pairs instead of once per pair.
+// device and each expert's pairs go through the tensor cores in tiles of 128 rows x 128 outputs, so an
+// expert's matrices are read once per 128 pairs instead of once per pair.
 //   hb_moe_group:   counts per expert, where each expert's pairs and tiles begin, the pairs listed by expert
 //   grouped product (mma.sync m16n8k16): rows gathered through the list; first product with the
 //                   activation into mid[pair], second product into part[pair] (float)
@@ -194,9 +194,10 @@ extern "C" int hb_moe_experts(int dtype, const void* h, int ld, const void* up, 
 // pair's own numbers do not depend on its place, so the result is the same bits every time.
 #include "mma_utils.cuh"
 
-#define MG_TM 64
-#define MG_TN 64
-#define MG_TK 64
+#define MG_TM 128
+#define MG_TN 128
+#define MG_TK 32
+#define MG_THREADS 256
 #define MG_MAX_EXPERTS 1024
 
 __global__ void __launch_bounds__(1024)
@@ -234,12 +235,11 @@ moe_group_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restric
 // C[pair, n] = sum_k A[row(pair), k] * W[e][n][k] for the pairs of tile blockIdx.x of its expert.
 // UP: row(pair) = pair / top of h, C = act(.) as bfloat16 into mid[pair]; else row(pair) = pair of mid, C float into part[pair].
 template <bool UP>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(MG_THREADS)
 moe_grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, void* __restrict__ C, int ldc,
                         const int* __restrict__ pair_off, const int* __restrict__ tile_off, const int* __restrict__ list, int E,
                         int N, int K, int top, int act) {
-  __shared__ __align__(16) bf16 As[2][MG_TM][MG_TK + 8];
-  __shared__ __align__(16) bf16 Ws[2][MG_TN][MG_TK + 8];
+  __shared__ __align__(16) bf16 AW[2][(MG_TM + MG_TN) * (MG_TK + 8)];      // per buffer: the A tile, then the W tile
   __shared__ int rows[MG_TM];
   pdl_wait();
   pdl_launch();
@@ -249,37 +249,50 @@ moe_grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restr
   while (tile >= tile_off[e + 1]) ++e;
   const int first = pair_off[e] + (tile - tile_off[e]) * MG_TM, end = pair_off[e + 1];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int wm = (warp & 3) * 32, wn = (warp >> 2) * 64;      // this warp's 32 rows x 64 outputs of the tile
   if (tid < MG_TM) rows[tid] = first + tid < end ? list[first + tid] : -1;
   __syncthreads();
   const int n0 = blockIdx.y * MG_TN;
   const bf16* We = W + (size_t)e * N * K;
 
+  // 128 rows x 4 pieces of 16 bytes for A and as many for W: 1,024 pieces, 4 per thread, the same (row, piece)
+  // in every k slab, so where each comes from is worked out once
+  constexpr int PIECES = 2 * MG_TM * (MG_TK / 8) / MG_THREADS;
+  const bf16* src0[PIECES];
+  int dst0[PIECES], kc[PIECES];
+#pragma unroll
+  for (int q = 0; q < PIECES; ++q) {
+    const int i = tid + q * MG_THREADS;
+    const bool isw = i >= MG_TM * (MG_TK / 8);
+    const int j = isw ? i - MG_TM * (MG_TK / 8) : i;
+    const int r = j / (MG_TK / 8), c = (j % (MG_TK / 8)) * 8;
+    kc[q] = c;
+    dst0[q] = (isw ? MG_TM * (MG_TK + 8) : 0) + r * (MG_TK + 8) + c;      // As and Ws of a buffer lie one after the other below
+    src0[q] = nullptr;
+    if (isw) {
+      if (n0 + r < N) src0[q] = We + (size_t)(n0 + r) * K + c;
+    } else if (rows[r] >= 0) {
+      src0[q] = A + (size_t)(UP ? rows[r] / top : rows[r]) * lda + c;
+    }
+  }
   auto load = [&](int buf, int k0) {
-    // 64 rows x MG_TK / 8 pieces of 16 bytes for A and as many for W
-    for (int i = tid; i < 2 * MG_TM * (MG_TK / 8); i += 128) {
-      const bool isw = i >= MG_TM * (MG_TK / 8);
-      const int j = isw ? i - MG_TM * (MG_TK / 8) : i;
-      const int r = j / (MG_TK / 8), c = (j % (MG_TK / 8)) * 8;
-      bf16* dst = isw ? &Ws[buf][r][c] : &As[buf][r][c];
-      const bf16* src = nullptr;
-      if (k0 + c < K) {
-        if (isw) {
-          if (n0 + r < N) src = We + (size_t)(n0 + r) * K + k0 + c;
-        } else if (rows[r] >= 0) {
-          src = A + (size_t)(UP ? rows[r] / top : rows[r]) * lda + k0 + c;
-        }
-      }
-      if (src) cp_async16(dst, src);
+    bf16* base = &AW[buf][0];
+#pragma unroll
+    for (int q = 0; q < PIECES; ++q) {
+      bf16* dst = base + dst0[q];
+      if (src0[q] && k0 + kc[q] < K) cp_async16(dst, src0[q] + k0);
       else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
     cp_async_commit();
   };
 
-  float acc[8][4];
+  float acc[2][8][4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int c = 0; c < 4; ++c) acc[i][c] = 0.0f;
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[m][i][c] = 0.0f;
   const int nk = (K + MG_TK - 1) / MG_TK;
   load(0, 0);
   for (int kb = 0; kb < nk; ++kb) {
@@ -293,33 +306,40 @@ moe_grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restr
     const int buf = kb & 1;
 #pragma unroll
     for (int ks = 0; ks < MG_TK / 16; ++ks) {
-      unsigned a0, a1, a2, a3;
-      ldmatrix_x4(a0, a1, a2, a3, &As[buf][warp * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+      unsigned a[2][4];
+#pragma unroll
+      for (int m = 0; m < 2; ++m)
+        ldmatrix_x4(a[m][0], a[m][1], a[m][2], a[m][3], &AW[buf][(wm + m * 16 + (lane & 15)) * (MG_TK + 8) + ks * 16 + (lane >> 4) * 8]);
 #pragma unroll
       for (int np = 0; np < 4; ++np) {
         unsigned b0, b1, b2, b3;
-        ldmatrix_x4(b0, b1, b2, b3, &Ws[buf][np * 16 + (lane & 7) + ((lane >> 4) << 3)][ks * 16 + ((lane >> 3) & 1) * 8]);
-        mma16816(acc[2 * np], a0, a1, a2, a3, b0, b1);
-        mma16816(acc[2 * np + 1], a0, a1, a2, a3, b2, b3);
+        ldmatrix_x4(b0, b1, b2, b3, &AW[buf][(MG_TM + wn + np * 16 + (lane & 7) + ((lane >> 4) << 3)) * (MG_TK + 8) + ks * 16 + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          mma16816(acc[m][2 * np], a[m][0], a[m][1], a[m][2], a[m][3], b0, b1);
+          mma16816(acc[m][2 * np + 1], a[m][0], a[m][1], a[m][2], a[m][3], b2, b3);
+        }
       }
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int pair = rows[warp * 16 + g + half * 8];
-    if (pair < 0) continue;
+  for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
+    for (int half = 0; half < 2; ++half) {
+      const int pair = rows[wm + m * 16 + g + half * 8];
+      if (pair < 0) continue;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int n = n0 + nt * 8 + 2 * t + c;
-        if (n >= N) continue;
-        const float v = acc[nt][half * 2 + c];
-        if (UP) ((bf16*)C)[(size_t)pair * ldc + n] = __float2bfloat16_rn(moe_act(v, act));
-        else ((float*)C)[(size_t)pair * ldc + n] = v;
-      }
-  }
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int n = n0 + wn + nt * 8 + 2 * t + c;
+          if (n >= N) continue;
+          const float v = acc[m][nt][half * 2 + c];
+          if (UP) ((bf16*)C)[(size_t)pair * ldc + n] = __float2bfloat16_rn(moe_act(v, act));
+          else ((float*)C)[(size_t)pair * ldc + n] = v;
+        }
+    }
 }
 
 __global__ void moe_combine_kernel(const float* __restrict__ part, const float* __restrict__ wts, float* __restrict__ y, int ldy,
@@ -354,9 +374,9 @@ extern "C" int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up
   cudaStream_t s = (cudaStream_t)stream;
   hb_launch(moe_group_kernel, dim3(1), dim3(1024), 0, s, ids, n_pairs, E, pair_off, tile_off, list);
   const int max_tiles = ceil_div(n_pairs, MG_TM) + E;
-  hb_launch(moe_grouped_gemm_kernel<true>, dim3(max_tiles, ceil_div(F, MG_TN)), dim3(128), 0, s, (const bf16*)h, ld, (const bf16*)up,
+  hb_launch(moe_grouped_gemm_kernel<true>, dim3(max_tiles, ceil_div(F, MG_TN)), dim3(MG_THREADS), 0, s, (const bf16*)h, ld, (const bf16*)up,
             mid, F, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, F, D, top, act);
-  hb_launch(moe_grouped_gemm_kernel<false>, dim3(max_tiles, ceil_div(D, MG_TN)), dim3(128), 0, s, (const bf16*)mid, F,
+  hb_launch(moe_grouped_gemm_kernel<false>, dim3(max_tiles, ceil_div(D, MG_TN)), dim3(MG_THREADS), 0, s, (const bf16*)mid, F,
             (const bf16*)down, (void*)part, D, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, D, F, top, act);
   hb_launch(moe_combine_kernel, dim3(ceil_div(D, 256), n_tokens), dim3(256), 0, s, (const float*)part, weights, y, ldy, D, top, accumulate);
   HB_CHECK_LAUNCH("moe_experts_grouped");
