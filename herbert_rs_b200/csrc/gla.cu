@@ -14,32 +14,52 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------------
-// a[t, c] = exp(logsigmoid(z) / tau),  z = b[c] + sum_r low[t, r] * W2[c, r].  One thread per (t, c).
+// a[t, c] = exp(logsigmoid(z) / tau),  z = b[c] + sum_r low[t, r] * W2[c, r].  A CTA takes GD_TOK tokens whose
+// low-rank rows it keeps in shared memory, and a thread one channel: it reads its row of W2 once for all of them.
+#define GD_TOK 8
+#define GD_THREADS 128
 template <typename T>
-__global__ void gla_decay_kernel(const float* __restrict__ low, int ld, const T* __restrict__ w2, const float* __restrict__ bias,
-                                 float inv_tau, float* __restrict__ a, int n_tokens, int C, int R) {
+__global__ void __launch_bounds__(GD_THREADS)
+gla_decay_kernel(const float* __restrict__ low, int ld, const T* __restrict__ w2, const float* __restrict__ bias,
+                 float inv_tau, float* __restrict__ a, int n_tokens, int C, int R) {
+  extern __shared__ float lows[];  // [GD_TOK][R]
   pdl_wait();
   pdl_launch();
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (long long)n_tokens * C) return;
-  const int t = (int)(idx / C), c = (int)(idx % C);
-  const float* lr = low + (size_t)t * ld;
+  const int t0 = blockIdx.y * GD_TOK, c = blockIdx.x * GD_THREADS + threadIdx.x;
+  const int nt = n_tokens - t0 < GD_TOK ? n_tokens - t0 : GD_TOK;
+  for (int i = threadIdx.x; i < nt * R; i += GD_THREADS) lows[i] = low[(size_t)(t0 + i / R) * ld + i % R];
+  __syncthreads();
+  if (c >= C) return;
   const T* wr = w2 + (size_t)c * R;
-  float z = bias ? bias[c] : 0.0f;
-  for (int r = 0; r < R; ++r) z = fmaf(lr[r], to_f32(wr[r]), z);
-  const float ls = fminf(z, 0.0f) - log1pf(expf(-fabsf(z)));  // log sigmoid(z)
-  a[idx] = expf(ls * inv_tau);
+  float z[GD_TOK];
+  const float b = bias ? bias[c] : 0.0f;
+#pragma unroll
+  for (int i = 0; i < GD_TOK; ++i) z[i] = b;
+  for (int r = 0; r < R; ++r) {
+    const float w = to_f32(wr[r]);
+#pragma unroll
+    for (int i = 0; i < GD_TOK; ++i)
+      if (i < nt) z[i] = fmaf(lows[i * R + r], w, z[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < GD_TOK; ++i)
+    if (i < nt) {
+      const float ls = fminf(z[i], 0.0f) - log1pf(expf(-fabsf(z[i])));  // log sigmoid(z)
+      a[(size_t)(t0 + i) * C + c] = expf(ls * inv_tau);
+    }
 }
 
 extern "C" int hb_gla_decay(int dtype, const float* low, int ld, const void* w2, const float* bias, float inv_tau, float* a,
                             int n_tokens, int channels, int low_rank, void* stream) {
   HB_REQUIRE(n_tokens > 0 && channels > 0 && low_rank > 0, "gla_decay: sizes must be positive");
-  const long long n = (long long)n_tokens * channels;
-  dim3 grid((unsigned)ceil_div_ll(n, 256));
+  HB_REQUIRE(ceil_div(n_tokens, GD_TOK) <= 65535, "gla_decay: too many tokens per call");
+  const size_t smem = (size_t)GD_TOK * low_rank * sizeof(float);
+  HB_REQUIRE(smem <= 48 * 1024, "gla_decay: the decay's inner width %d exceeds what a block keeps in shared memory", low_rank);
+  dim3 grid(ceil_div(channels, GD_THREADS), ceil_div(n_tokens, GD_TOK));
   if (dtype == HB_F32)
-    hb_launch(gla_decay_kernel<float>, grid, dim3(256), 0, (cudaStream_t)stream, low, ld, (const float*)w2, bias, inv_tau, a, n_tokens, channels, low_rank);
+    hb_launch(gla_decay_kernel<float>, grid, dim3(GD_THREADS), smem, (cudaStream_t)stream, low, ld, (const float*)w2, bias, inv_tau, a, n_tokens, channels, low_rank);
   else
-    hb_launch(gla_decay_kernel<bf16>, grid, dim3(256), 0, (cudaStream_t)stream, low, ld, (const bf16*)w2, bias, inv_tau, a, n_tokens, channels, low_rank);
+    hb_launch(gla_decay_kernel<bf16>, grid, dim3(GD_THREADS), smem, (cudaStream_t)stream, low, ld, (const bf16*)w2, bias, inv_tau, a, n_tokens, channels, low_rank);
   HB_CHECK_LAUNCH("gla_decay");
   return 0;
 }

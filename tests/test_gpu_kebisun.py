@@ -57,6 +57,23 @@ def test_layer_norm_alone_and_with_the_scaled_residual_sum(dtype, dim):
     assert_close(to_np(x3), ref.numpy(), "float32", "without scale")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter,interleave", [(40, 8), (24, 0), (30, 0)])
+@pytest.mark.parametrize("act", ["gelu_tanh", "gelu", "silu"])
+def test_gated_activation_kernel(dtype, inter, interleave, act):
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+    g = torch.Generator().manual_seed(inter)
+    gate, up = (torch.randn(9, inter, generator=g) * 2).to(td), torch.randn(9, inter, generator=g).to(td)
+    if interleave:
+        gu = torch.cat([gate.view(9, -1, 1, 8), up.view(9, -1, 1, 8)], dim=2).reshape(9, 2 * inter)
+    else:
+        gu = torch.cat([gate, up], dim=1)
+    out = torch.empty(9, inter, dtype=td, device=DEV)
+    ops.swiglu(gu.contiguous().to(DEV), out, interleave, ops.ACTIVATIONS[act])
+    f = {"gelu_tanh": P.gelu_tanh, "gelu": P.gelu_erf, "silu": P.silu}[act]
+    assert_close(to_np(out), (f(gate.double()) * up.double()).numpy(), dtype, act)
+
+
 @pytest.mark.parametrize("scaling", [True, False])
 def test_rotation_with_stretched_frequencies(scaling):
     from herbert_rs_b200.config.specs import ScaledRotarySpec
