@@ -390,15 +390,16 @@ extern "C" int hb_latent_attention(int dtype, const float* q, int ldq, float* ou
 // heads share one cached vector per token, the rows of the score matrix are (token, head) pairs, head
 // fastest: a CTA takes 32 consecutive pairs of one sequence (with 16 heads: two tokens; a decode step:
 // all heads of the one token) against 64 keys at a time.
-//   phase 1: S = Q K^T, 32 x 64 over W = rank + rot: warp w owns rows 16 (w & 1).., keys 16 (w >> 1)..
+//   phase 1: S = Q K^T, 32 x 64 over W = rank + rot: warp w owns rows 16 (w & 1).., keys 8 (w >> 1)..
 //   softmax: per-row maxima and sums meet in shared memory; P (bfloat16) goes to shared memory
 //   phase 2: O += P C, 32 x rank: the key tile's first `rank` columns are the values; warp w owns the
-//            16-column groups w, w + 8, ... of O for all 32 rows
+//            16-column groups w, w + 16, ... of O for all 32 rows
 // Key tiles go global -> shared with cp.async, two buffers; a row of a tile finds its own page, so any
 // page size serves.  Masked scores never enter a maximum or a sum; the sink starts m and l.
 #define LM_ROWS 32
 #define LM_KEYS 64
-#define LM_WARPS 8
+#define LM_WARPS 16
+#define LM_KG 8            // key groups of 8 keys per round of 64
 #define LM_THREADS (LM_WARPS * 32)
 #define LM_NEG (-1.0e30f)
 
@@ -419,7 +420,7 @@ struct LatentMmaArgs {
   int row_tiles;
 };
 
-template <int NPW>  // 16-column groups of O per warp: rank <= 128 * NPW
+template <int NPW>  // 16-column groups of O per warp: rank <= 256 * NPW
 __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(LatentMmaArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
   pdl_wait();
@@ -428,9 +429,9 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
   unsigned char* qs = smem;
   unsigned char* kbuf = qs + LM_ROWS * rb;
   unsigned char* ps = kbuf + 2 * LM_KEYS * rb;
-  float* smax = (float*)(ps + LM_ROWS * pb);   // [32][4]
-  float* ssum = smax + LM_ROWS * 4;            // [32][4]
-  float* mrow = ssum + LM_ROWS * 4;            // [32]
+  float* smax = (float*)(ps + LM_ROWS * pb);   // [32][LM_KG]
+  float* ssum = smax + LM_ROWS * LM_KG;        // [32][LM_KG]
+  float* mrow = ssum + LM_ROWS * LM_KG;        // [32]
   float* lrow = mrow + LM_ROWS;                // [32]
   int* rowp = (int*)(lrow + LM_ROWS);          // [32] position of the row's token (-1: no row)
   int* rowlo = rowp + LM_ROWS;                 // [32] first key the row sees
@@ -495,6 +496,12 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
         for (int c = 0; c < 4; ++c) acc[i][j][k][c] = 0.0f;
   const int npairs = a.rank >> 4;
   const int mt = warp & 1, kg = warp >> 1;
+  auto row_max = [&](int r) {       // the row's maximum so far and over this round's key groups
+    float m = mrow[r];
+#pragma unroll
+    for (int k = 0; k < LM_KG; ++k) m = fmaxf(m, smax[r * LM_KG + k]);
+    return m;
+  };
 
   if (it0 < it1) load_tile(it0);
   for (int it = it0; it < it1; ++it) {
@@ -506,79 +513,71 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
     }
     __syncthreads();
     const unsigned char* kt = kbuf + (it & 1) * LM_KEYS * rb;
-    // ---- phase 1: scores of rows 16 mt.. against keys 16 kg..
-    // four sets of partial sums over k, so that four instructions per score tile are in flight, not one after the other
-    float s[2][4], sp[4][2][4];
+    // ---- phase 1: scores of rows 16 mt.. against keys 8 kg..; four sets of partial sums over k, so that
+    // four instructions per score tile are in flight, not one after the other
+    float s[4], sp[4][4];
 #pragma unroll
     for (int u = 0; u < 4; ++u)
 #pragma unroll
-      for (int i = 0; i < 2; ++i)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) sp[u][i][c] = 0.0f;
+      for (int c = 0; c < 4; ++c) sp[u][c] = 0.0f;
     {
       const unsigned char* qa = qs + (mt * 16 + (lane & 15)) * rb + (lane >> 4) * 16;
-      const unsigned char* kb = kt + (kg * 16 + (lane & 7) + ((lane >> 4) << 3)) * rb + ((lane >> 3) & 1) * 16;
+      const unsigned char* kb = kt + (kg * 8 + (lane & 7)) * rb + (lane >> 3) * 16;   // one load: these 8 keys, 32 of k
       const int nks = W >> 4;
       int ks = 0;
       for (; ks + 4 <= nks; ks += 4) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 2; ++u) {
           unsigned a0, a1, a2, a3, b0, b1, b2, b3;
-          ldmatrix_x4(a0, a1, a2, a3, qa + (ks + u) * 32);
-          ldmatrix_x4(b0, b1, b2, b3, kb + (ks + u) * 32);
-          mma16816(sp[u][0], a0, a1, a2, a3, b0, b1);
-          mma16816(sp[u][1], a0, a1, a2, a3, b2, b3);
+          ldmatrix_x4(b0, b1, b2, b3, kb + (ks + 2 * u) * 32);
+          ldmatrix_x4(a0, a1, a2, a3, qa + (ks + 2 * u) * 32);
+          mma16816(sp[2 * u], a0, a1, a2, a3, b0, b1);
+          ldmatrix_x4(a0, a1, a2, a3, qa + (ks + 2 * u + 1) * 32);
+          mma16816(sp[2 * u + 1], a0, a1, a2, a3, b2, b3);
         }
       }
-      for (; ks < nks; ++ks) {
+      for (; ks < nks; ++ks) {      // what is left, a step of 16 at a time (the load's upper half is not used)
         unsigned a0, a1, a2, a3, b0, b1, b2, b3;
-        ldmatrix_x4(a0, a1, a2, a3, qa + ks * 32);
         ldmatrix_x4(b0, b1, b2, b3, kb + ks * 32);
-        mma16816(sp[0][0], a0, a1, a2, a3, b0, b1);
-        mma16816(sp[0][1], a0, a1, a2, a3, b2, b3);
+        ldmatrix_x4(a0, a1, a2, a3, qa + ks * 32);
+        mma16816(sp[0], a0, a1, a2, a3, b0, b1);
       }
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) s[i][c] = (sp[0][i][c] + sp[1][i][c]) + (sp[2][i][c] + sp[3][i][c]);
-    const int jb = k0 + it * LM_KEYS + kg * 16 + 2 * t;
+    for (int c = 0; c < 4; ++c) s[c] = (sp[0][c] + sp[1][c]) + (sp[2][c] + sp[3][c]);
+    const int jb = k0 + it * LM_KEYS + kg * 8 + 2 * t;
     const int ra = mt * 16 + g, rbw = ra + 8;
     const int pa = rowp[ra], la = rowlo[ra], pbv = rowp[rbw], lb = rowlo[rbw];
-    bool ok[2][4];
+    bool ok[4];
     float mxa = LM_NEG, mxb = LM_NEG;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int j = jb + nt * 8 + (c & 1);
-        const bool o = c < 2 ? (j >= la && j <= pa) : (j >= lb && j <= pbv);
-        ok[nt][c] = o;
-        if (o) {
-          if (c < 2) mxa = fmaxf(mxa, s[nt][c]); else mxb = fmaxf(mxb, s[nt][c]);
-        }
+    for (int c = 0; c < 4; ++c) {
+      const int j = jb + (c & 1);
+      const bool o = c < 2 ? (j >= la && j <= pa) : (j >= lb && j <= pbv);
+      ok[c] = o;
+      if (o) {
+        if (c < 2) mxa = fmaxf(mxa, s[c]); else mxb = fmaxf(mxb, s[c]);
       }
+    }
     mxa = fmaxf(mxa, __shfl_xor_sync(0xffffffffu, mxa, 1));
     mxa = fmaxf(mxa, __shfl_xor_sync(0xffffffffu, mxa, 2));
     mxb = fmaxf(mxb, __shfl_xor_sync(0xffffffffu, mxb, 1));
     mxb = fmaxf(mxb, __shfl_xor_sync(0xffffffffu, mxb, 2));
     if (t == 0) {
-      smax[ra * 4 + kg] = mxa;
-      smax[rbw * 4 + kg] = mxb;
+      smax[ra * LM_KG + kg] = mxa;
+      smax[rbw * LM_KG + kg] = mxb;
     }
     __syncthreads();
-    const float ma = fmaxf(mrow[ra], fmaxf(fmaxf(smax[ra * 4], smax[ra * 4 + 1]), fmaxf(smax[ra * 4 + 2], smax[ra * 4 + 3])));
-    const float mb = fmaxf(mrow[rbw], fmaxf(fmaxf(smax[rbw * 4], smax[rbw * 4 + 1]), fmaxf(smax[rbw * 4 + 2], smax[rbw * 4 + 3])));
-    float sa = 0.0f, sb = 0.0f;
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const float p0 = ok[nt][0] ? expf(s[nt][0] - ma) : 0.0f, p1 = ok[nt][1] ? expf(s[nt][1] - ma) : 0.0f;
-      const float p2 = ok[nt][2] ? expf(s[nt][2] - mb) : 0.0f, p3 = ok[nt][3] ? expf(s[nt][3] - mb) : 0.0f;
+    const float ma = row_max(ra), mb = row_max(rbw);
+    float sa, sb;
+    {
+      const float p0 = ok[0] ? expf(s[0] - ma) : 0.0f, p1 = ok[1] ? expf(s[1] - ma) : 0.0f;
+      const float p2 = ok[2] ? expf(s[2] - mb) : 0.0f, p3 = ok[3] ? expf(s[3] - mb) : 0.0f;
       // the sums take the rounded weights, the ones the product below uses
       const __nv_bfloat162 ua = __floats2bfloat162_rn(p0, p1), ub = __floats2bfloat162_rn(p2, p3);
-      sa += __bfloat162float(ua.x) + __bfloat162float(ua.y);
-      sb += __bfloat162float(ub.x) + __bfloat162float(ub.y);
-      const int col = kg * 16 + nt * 8 + 2 * t;
+      sa = __bfloat162float(ua.x) + __bfloat162float(ua.y);
+      sb = __bfloat162float(ub.x) + __bfloat162float(ub.y);
+      const int col = kg * 8 + 2 * t;
       *(__nv_bfloat162*)(ps + ra * pb + col * 2) = ua;
       *(__nv_bfloat162*)(ps + rbw * pb + col * 2) = ub;
     }
@@ -587,17 +586,15 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
     sb += __shfl_xor_sync(0xffffffffu, sb, 1);
     sb += __shfl_xor_sync(0xffffffffu, sb, 2);
     if (t == 0) {
-      ssum[ra * 4 + kg] = sa;
-      ssum[rbw * 4 + kg] = sb;
+      ssum[ra * LM_KG + kg] = sa;
+      ssum[rbw * LM_KG + kg] = sb;
     }
     __syncthreads();
     // ---- phase 2: O = O * corr + P C for this warp's column groups, both row tiles
 #pragma unroll
     for (int m2 = 0; m2 < 2; ++m2) {
       const int r1 = m2 * 16 + g, r2 = r1 + 8;
-      const float n1 = fmaxf(mrow[r1], fmaxf(fmaxf(smax[r1 * 4], smax[r1 * 4 + 1]), fmaxf(smax[r1 * 4 + 2], smax[r1 * 4 + 3])));
-      const float n2 = fmaxf(mrow[r2], fmaxf(fmaxf(smax[r2 * 4], smax[r2 * 4 + 1]), fmaxf(smax[r2 * 4 + 2], smax[r2 * 4 + 3])));
-      const float c1 = expf(mrow[r1] - n1), c2 = expf(mrow[r2] - n2);
+      const float c1 = expf(mrow[r1] - row_max(r1)), c2 = expf(mrow[r2] - row_max(r2));
 #pragma unroll
       for (int j = 0; j < NPW; ++j)
 #pragma unroll
@@ -629,9 +626,11 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(Latent
     }
     __syncthreads();
     if (tid < LM_ROWS) {
-      const float mo = mrow[tid];
-      const float mn = fmaxf(mo, fmaxf(fmaxf(smax[tid * 4], smax[tid * 4 + 1]), fmaxf(smax[tid * 4 + 2], smax[tid * 4 + 3])));
-      lrow[tid] = lrow[tid] * expf(mo - mn) + (ssum[tid * 4] + ssum[tid * 4 + 1] + ssum[tid * 4 + 2] + ssum[tid * 4 + 3]);
+      const float mo = mrow[tid], mn = row_max(tid);
+      float sum = 0.0f;
+#pragma unroll
+      for (int k = 0; k < LM_KG; ++k) sum += ssum[tid * LM_KG + k];
+      lrow[tid] = lrow[tid] * expf(mo - mn) + sum;
       mrow[tid] = mn;
     }
   }
@@ -702,7 +701,7 @@ latent_attention_join_kernel(const float* __restrict__ part, float* __restrict__
 
 static size_t latent_mma_smem(int W) {
   const size_t rb = (size_t)W * 2 + 16;
-  return (LM_ROWS + 2 * LM_KEYS) * rb + LM_ROWS * (LM_KEYS * 2 + 16) + LM_ROWS * 12 * sizeof(float);
+  return (LM_ROWS + 2 * LM_KEYS) * rb + LM_ROWS * (LM_KEYS * 2 + 16) + LM_ROWS * (2 * LM_KG + 4) * sizeof(float);
 }
 
 // Whether the tensor-core kernel serves these sizes (else the any-shape kernel does).
@@ -734,7 +733,7 @@ extern "C" int hb_latent_attention_mma_bf16(const float* q, int ldq, float* out,
     cudaFuncSetAttribute(latent_attention_mma_kernel<NPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
     hb_launch(latent_attention_mma_kernel<NPW>, grid, dim3(LM_THREADS), smem, s, a);                                   \
   } while (0)
-  if (rank <= 128) LM_GO(1); else if (rank <= 256) LM_GO(2); else LM_GO(4);
+  if (rank <= 256) LM_GO(1); else LM_GO(2);
 #undef LM_GO
   if (nsplit > 1)
     hb_launch(latent_attention_join_kernel, dim3(max_q_len * heads, n_seqs), dim3(LJ_THREADS), 0, s, (const float*)scratch, out, ldo,
