@@ -82,7 +82,7 @@ __device__ __forceinline__ void gla_copy16(float* smem, const float* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem));
 }
 
-template <int RPT, int COLS>  // rows per thread: dk <= (128 / COLS) * RPT
+template <int RPT, int COLS>  // rows per thread: dk <= (128 / COLS) * RPT; up to 1,024 key channels with 8 columns
 __global__ void __launch_bounds__(GLA_THREADS)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                 float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
@@ -195,7 +195,7 @@ extern "C" int hb_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
                            const int* seq_slot, const int* seq_start, float* out, int ldo, int n_seqs, int heads, int dk,
                            int dv, float qscale, void* stream) {
   HB_REQUIRE(n_seqs > 0 && heads > 0 && dk > 0 && dv > 0, "gla_scan: sizes must be positive");
-  HB_REQUIRE(dk <= 4 * 64, "gla_scan: %d key channels per head exceed the supported maximum 256", dk);
+  HB_REQUIRE(dk <= 16 * 64, "gla_scan: %d key channels per head exceed the supported maximum 1024", dk);
   HB_REQUIRE(heads <= 65535 && ceil_div(dv, 8) <= 65535, "gla_scan: too many heads or value channels");
   cudaStream_t s = (cudaStream_t)stream;
   const int wide = dk % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && (((uintptr_t)proj | (uintptr_t)decay) & 15) == 0;
@@ -203,14 +203,16 @@ extern "C" int hb_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
   int sms = 0, dev = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  int cols = 32;
+  int cols = dk > 512 ? 8 : dk > 256 ? 16 : 32;                    // at most 64 state rows per thread
   while (cols > 8 && (long long)n_seqs * heads * ceil_div(dv, cols) < sms) cols >>= 1;
   const int groups = GLA_THREADS / cols;
   int rpt = ceil_div(ceil_div(dk, groups), 4) * 4;                 // rows per thread, whole float4s
   rpt = rpt <= 4 ? 4 : rpt <= 8 ? 8 : rpt <= 16 ? 16 : rpt <= 32 ? 32 : 64;
-  const int chunk = 16;     // tokens per stage: enough work per stage to cover the next stage's way from memory
+  // tokens per stage: enough work per stage to cover the next stage's way from memory, within 100 KB of shared memory
+  const size_t per_token = (size_t)(2 * (3 * groups * rpt + cols) + GLA_THREADS) * sizeof(float);
+  const int chunk = (int)(100 * 1024 / per_token) >= 16 ? 16 : ((int)(100 * 1024 / per_token) < 1 ? 1 : (int)(100 * 1024 / per_token));
   dim3 grid(n_seqs, heads, ceil_div(dv, cols)), block(cols, groups);
-  const size_t smem = (size_t)chunk * (2 * (3 * groups * rpt + cols) + GLA_THREADS) * sizeof(float);
+  const size_t smem = (size_t)chunk * per_token;
 #define GLA_GO(RPT, COLS)                                                                                                       \
   do {                                                                                                                          \
     if (smem > 48 * 1024) cudaFuncSetAttribute(gla_scan_kernel<RPT, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
@@ -224,10 +226,7 @@ extern "C" int hb_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
     else GLA_GO(RPT, 8);                                    \
   } while (0)
   if (rpt == 4) GLA_COLS(4); else if (rpt == 8) GLA_COLS(8); else if (rpt == 16) GLA_COLS(16); else if (rpt == 32) GLA_COLS(32);
-  else {
-    HB_REQUIRE(cols == 32, "gla_scan: internal: 64 rows per thread only with 32 columns");
-    GLA_GO(64, 32);
-  }
+  else GLA_COLS(64);
 #undef GLA_COLS
 #undef GLA_GO
   HB_CHECK_LAUNCH("gla_scan");

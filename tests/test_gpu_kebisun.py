@@ -365,7 +365,7 @@ OTHER = {
                          (K.gla(heads=1, dim=8, vdim=8, tau=1.0), None)],
     "wide_heads": [(K.gla(heads=2, dim=72, vdim=100), K.moe(experts=9, top=9, ff=40)),
                    (K.latent(heads=5, dim=40, rot=24, vdim=48, kv_rank=136, q_rank=72, window=100), K.dense(ff=200))],
-    "gla_only": [(K.gla(), K.dense()), (K.gla(heads=4, dim=130, vdim=33), K.dense())],
+    "gla_only": [(K.gla(), K.dense()), (K.gla(heads=4, dim=130, vdim=33), K.dense()), (K.gla(heads=1, dim=300, vdim=20), None)],
     "latent_only": [(K.latent(rot=16, dim=8), K.moe()), (K.latent(kv_rank=16, vdim=72, window=300), K.moe())],
 }
 
