@@ -366,6 +366,8 @@ OTHER = {
     "wide_heads": [(K.gla(heads=2, dim=72, vdim=100), K.moe(experts=9, top=9, ff=40)),
                    (K.latent(heads=5, dim=40, rot=24, vdim=48, kv_rank=136, q_rank=72, window=100), K.dense(ff=200))],
     "gla_only": [(K.gla(), K.dense()), (K.gla(heads=4, dim=130, vdim=33), K.dense()), (K.gla(heads=1, dim=300, vdim=20), None)],
+    "odd_sizes": [(K.latent(heads=3, dim=10, rot=6, vdim=6, kv_rank=20, q_rank=14, window=33), K.dense(ff=30)),
+                  (K.gla(heads=3, dim=10, vdim=14, tau=5.0), K.moe(experts=3, top=2, ff=12))],
     "latent_only": [(K.latent(rot=16, dim=8), K.moe()), (K.latent(kv_rank=16, vdim=72, window=300), K.moe())],
 }
 
@@ -373,8 +375,9 @@ OTHER = {
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("which", sorted(OTHER))
 def test_other_sizes_and_orders(tmp_path, which, dtype):
-    kw = dict(vocab=77, width=40, emb_scale=1.0, eps=1e-6) if which == "one_head_top_one" else dict(vocab=300, width=136)
-    d, pm = K.make(tmp_path / which, OTHER[which], seed=7, decay_rank=3 if which == "gla_only" else 16, **kw)
+    kw = dict(vocab=77, width=40, emb_scale=1.0, eps=1e-6) if which == "one_head_top_one" else \
+        dict(vocab=61, width=50) if which == "odd_sizes" else dict(vocab=300, width=136)
+    d, pm = K.make(tmp_path / which, OTHER[which], seed=7, decay_rank=3 if which in ("gla_only", "odd_sizes") else 16, **kw)
     rng = np.random.default_rng(5)
     reqs = [ids_for(rng, kw["vocab"], n) for n in (130, 2, 66)]
     refs = [pm.logits(r).numpy() for r in reqs]
