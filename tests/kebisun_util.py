@@ -16,7 +16,6 @@ import os
 
 import torch
 
-import herbert_rs_b200 as hb
 from herbert_rs_b200.weights.safetensors_io import save_file
 
 
