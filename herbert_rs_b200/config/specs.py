@@ -20,12 +20,14 @@ from typing import Optional, Sequence
 @dataclass(frozen=True)
 class NormSpec:
     """A normalisation over the last axis.  kind "rmsnorm": y = x / sqrt(mean(x^2) + eps) * w;
-    kind "layernorm": y = (x - mean(x)) / sqrt(var(x) + eps) * w (no bias)."""
+    kind "layernorm": y = (x - mean(x)) / sqrt(var(x) + eps) * w (no bias).  `weight_offset` c: the
+    stored tensor is w - c (a weight kept around zero with c = 1), so the factor is c + stored."""
 
     dim: int
     eps: float
     kind: str = "rmsnorm"
     weight_name: str = "weight"     # the weight's tensor name under the part's prefix
+    weight_offset: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -99,7 +101,18 @@ class GatedLinearAttentionSpec:
 
 @dataclass(frozen=True)
 class AttentionSpec:
-    """Grouped-query softmax attention over cached keys and values."""
+    """Grouped-query softmax attention over cached keys and values.
+
+    Options beyond the plain form (each off by default):
+    `bias`: q, k (and v) = W h + b, the bias tensors named as the matrices with `bias_suffix` added;
+    `values_are_keys`: no value product: a head's values are its keys as projected, and the cache
+        keeps one plane;
+    `q_temperature` (coef, every): the query at position p is multiplied by
+        1 + coef * ln(floor((p + 1) / every) + 1);
+    `softcap` c: score <- c * tanh(score / c) after the scale;
+    `sink`: a learned number per query head (tensor `names[4]`) whose exponential joins the softmax's
+        denominator; it has no key and no value.
+    `names`: the tensors of q, k, v, o and the sink under the mixer's prefix."""
 
     hidden_size: int
     num_heads: int
@@ -110,6 +123,13 @@ class AttentionSpec:
     position: Optional[PositionSpec] = None
     window: Optional[int] = None  # None: every earlier key; n: the last n keys (itself included)
     kind: str = "attention"
+    bias: bool = False
+    bias_suffix: str = ".b"
+    values_are_keys: bool = False
+    q_temperature: Optional[tuple] = None
+    softcap: Optional[float] = None
+    sink: bool = False
+    names: tuple = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "sink")
 
 
 @dataclass(frozen=True)
@@ -129,7 +149,14 @@ class RoutedFFSpec:
     """A mixture of small feed-forwards down(act(up(x))) without biases: a token uses the `top_k`
     experts with the largest softmax(router x) (taken over all experts), weighted by those values,
     divided by their sum only with `renormalize`.  Tensor names: `router_name`, and
-    `expert_names` formatted with the expert's index for up and down."""
+    `expert_names` formatted with the expert's index for up and down.
+
+    Options: `gated`: an expert is down(act(gate(x)) * up(x)) and `expert_names` holds gate, up, down;
+    `score` "sigmoid": the scores are sigmoid(router x) instead of the softmax; `groups`, `keep_groups`,
+    `group_top`: the experts form `groups` equal groups of neighbours, a group's score is the sum of its
+    `group_top` largest scores, and only experts of the `keep_groups` best groups can be chosen;
+    `weight_scale`: a factor on every chosen weight; `shared`: a dense gated feed-forward (its own
+    spec, tensors under `shared_prefix`) that runs for every token and is added."""
 
     hidden_size: int
     num_experts: int
@@ -140,6 +167,13 @@ class RoutedFFSpec:
     router_name: str = "router"
     expert_names: tuple = ("e{e}.up", "e{e}.down")
     kind: str = "moe"
+    gated: bool = False
+    score: str = "softmax"
+    groups: int = 1
+    keep_groups: int = 1
+    group_top: int = 2
+    weight_scale: float = 1.0
+    shared: Optional[SwiGLUSpec] = None
 
 
 @dataclass(frozen=True)
@@ -150,15 +184,18 @@ class BlockSpec:
     kind "sublayer_norm": h = x + s1 * norm1(mixer(x)); out = h + s2 * norm2(ffn(h)): the sublayers
     read the stream itself and their results are normed; s1, s2 are per-channel scales named by
     `layer_scale` (None: no scales); `ffn` may be None (then the layer ends after the mixer).
+    kind "parallel": h = norm1(x); out = x + residual_mult * (mixer(h) + ffn(h)): one norm, both
+    sublayers read its result; `ffn` may be None; norm2 is unused (None).
     `names` maps the block's local part names to the sub-prefixes used in tensor names.
     """
 
     mixer: object
     ffn: object
     norm1: NormSpec
-    norm2: NormSpec
+    norm2: Optional[NormSpec]
     kind: str = "prenorm"
     layer_scale: Optional[tuple] = None
+    residual_mult: float = 1.0
     names: tuple = (
         ("norm1", "input_layernorm"),
         ("mixer", "self_attn"),
@@ -203,6 +240,9 @@ class ModelSpec:
     # which default to the token's index in its sequence in every component.
     position_components: int = 1
     embedding_scale: float = 1.0                  # the embedding rows are multiplied by this
+    # A learned vector per position, [max_position, hidden], added (unscaled) to the embedding row;
+    # None: the model has none.  A sequence cannot grow beyond the table.
+    position_table_name: Optional[str] = None
     extra: dict = field(default_factory=dict)     # free for an architecture's own model class
 
 

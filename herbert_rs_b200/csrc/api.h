@@ -47,12 +47,12 @@ int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens, void* out
 
 // attention_simt.cu: attention of any shape on the CUDA cores (the 32-bit path)
 int hb_attention_simt(int dtype, const void* q, int ldq, void* out, int ldo, const void* kcache, const void*
-    vcache, const int* tok_seq, const int* tok_pos, const int* seq_pages, int pages_stride, int n_tokens, int
-    nh, int nkv, int hd, int page_size, float scale, int window, void* stream);
+    vcache, const int* tok_seq, const int* tok_pos, const int* seq_pages, int pages_stride, int n_tokens, int nh, int
+    nkv, int hd, int page_size, float scale, int window, float softcap, const float* sink, void* stream);
 
 // elementwise.cu: embedding, RMSNorm, SwiGLU, head norm + rotation + cache write, residual sum, shared-norm finish
-int hb_embed(int dtype, const void* table, const int* ids, float* out, int n_tokens, int hidden, int vocab,
-    float scale, void* stream);
+int hb_embed(int dtype, const void* table, const int* ids, float* out, int n_tokens, int hidden, int vocab, float
+    scale, const void* pos_table, const int* positions, int n_positions, void* stream);
 int hb_rmsnorm(int dtype, const float* x, const float* w, void* out, const int* rows, int n_rows, int dim,
     float eps, void* stream);
 int hb_swiglu(int dtype, const void* gu, int ld, void* out, int ldo, int n_tokens, int inter, int interleave,
@@ -149,16 +149,26 @@ int hb_layernorm(int dtype, const float* x, const float* w, void* out, const int
 int hb_layernorm_residual(int dtype, const float* y, int ldy, const float* w, const float* scale, float* x, void*
     h, int n_rows, int dim, float eps, void* stream);
 
-// moe.cu: routed feed-forward: router with softmax and choice, the chosen experts' two products
-int hb_moe_route(int dtype, const void* h, int ld, const void* w_router, int* ids, float* weights, int
-    n_tokens, int D, int E, int top, int renorm, void* stream);
+// moe.cu: routed feed-forward: router (softmax or sigmoid scores, groups of experts) and choice, the chosen experts' products (plain or gated)
+int hb_moe_route(int dtype, const void* h, int ld, const void* w_router, int* ids, float* weights, int n_tokens,
+    int D, int E, int top, int renorm, int sigmoid, int groups, int keep, int group_top, float wscale, void* stream);
 int hb_moe_experts(int dtype, const void* h, int ld, const void* up, const void* down, const int* ids, const
-    float* weights, void* mid, float* y, int ldy, int n_tokens, int D, int F, int top, int act, int accumulate,
-    void* stream);
+    float* weights, void* mid, float* y, int ldy, int n_tokens, int D, int F, int top, int act, int gated, int
+    accumulate, void* stream);
 long long hb_moe_grouped_scratch_ints(int n_tokens, int E, int top);
 int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up, const void* down, const int* ids, const
-    float* weights, int* scratch, void* mid, float* part, float* y, int ldy, int n_tokens, int D, int E, int F,
-    int top, int act, int accumulate, void* stream);
+    float* weights, int* scratch, void* mid, float* part, float* y, int ldy, int n_tokens, int D, int E, int F, int
+    top, int act, int gated, int accumulate, void* stream);
+
+// qk_prepare.cu: biases, query temperature and cache write for a mixer that neither norms nor rotates its heads
+int hb_qk_prepare_cache(int dtype, const float* qkv, int ld, const float* bias, void* q_out, int ldq, float
+    temp_coef, int temp_every, const int* tok_seq, const int* tok_pos, const int* seq_pages, int pages_stride,
+    void* kcache, void* vcache, int n_tokens, int nh, int nkv, int hd, int page_size, int write_cache,
+    void* stream);
+
+// residual_norm.cu: x += mult * y, and the next block's RMS norm of the updated row
+int hb_scaled_residual_norm(int dtype, const float* y, int ldy, float mult, float* x, const float* w, void* h,
+    int n_rows, int dim, float eps, void* stream);
 
 // sampling.cu: argmax and temperature / top-k / top-p sampling
 int hb_argmax(const float* logits, int ld, int n_rows, int vocab, int* out, void* scratch, long long

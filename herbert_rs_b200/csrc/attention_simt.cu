@@ -9,6 +9,10 @@
 // here taken 32 keys at a time.  Range of the query at position p: keys lo..p with
 // lo = max(0, p - window + 1) when window > 0, else 0 (causal; decode.rs:126-295 scans 0..=pos).
 // Query head h reads key/value head h / (nh/nkv) (loader_common.rs:1003-1005).
+// Two options for other designs: a cap on the scores, s <- cap * tanh(s / cap) after the scale
+// (softcap > 0), and a sink, a learned number per query head whose exponential joins the softmax's
+// denominator and nothing else: the running maximum starts at the sink and the running sum at 1,
+// as if it were a first key without a value.  The value plane may be the key plane itself.
 #include "api.h"
 #include "common.cuh"
 
@@ -29,6 +33,8 @@ struct AttnArgs {
   int n_tokens, nh, nkv, hd, page_size;
   float scale;
   int window;
+  float softcap;
+  const float* sink;
 };
 
 template <typename T>
@@ -50,6 +56,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_simt_kernel(AttnArgs
   const size_t head_stride = (size_t)a.page_size * a.hd;
 
   float m = -INFINITY, l = 0.0f;
+  if (a.sink != nullptr) { m = a.sink[h]; l = 1.0f; }
   float o[ATT_MAX_HD / 32];
 #pragma unroll
   for (int i = 0; i < ATT_MAX_HD / 32; ++i) o[i] = 0.0f;
@@ -63,6 +70,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_simt_kernel(AttnArgs
       float dot = 0.0f;
       for (int d = 0; d < a.hd; ++d) dot = fmaf(qs[warp][d], to_f32(kr[d]), dot);
       s = dot * a.scale;
+      if (a.softcap > 0.0f) s = a.softcap * tanhf(s / a.softcap);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);  // m = -inf on the first chunk: exp(-inf) = 0
@@ -96,13 +104,15 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_simt_kernel(AttnArgs
 extern "C" int hb_attention_simt(int dtype, const void* q, int ldq, void* out, int ldo, const void* kcache,
                                  const void* vcache, const int* tok_seq, const int* tok_pos,
                                  const int* seq_pages, int pages_stride, int n_tokens, int nh, int nkv,
-                                 int hd, int page_size, float scale, int window, void* stream) {
+                                 int hd, int page_size, float scale, int window, float softcap, const float* sink,
+                                 void* stream) {
   HB_REQUIRE(n_tokens > 0 && nh > 0 && nkv > 0 && hd > 0 && page_size > 0, "attention: sizes must be positive");
   HB_REQUIRE(nh % nkv == 0, "attention: %d query heads are not a multiple of %d key/value heads", nh, nkv);
   HB_REQUIRE(hd <= ATT_MAX_HD, "attention: head size %d exceeds the supported maximum %d", hd, ATT_MAX_HD);
   HB_REQUIRE(window >= 0, "attention: window must be >= 0");
+  HB_REQUIRE(softcap >= 0.0f, "attention: the cap on the scores must be >= 0 (0: none)");
   AttnArgs a{q, ldq, out, ldo, kcache, vcache, tok_seq, tok_pos, seq_pages, pages_stride,
-             n_tokens, nh, nkv, hd, page_size, scale, window};
+             n_tokens, nh, nkv, hd, page_size, scale, window, softcap, sink};
   const long long blocks = ceil_div_ll((long long)n_tokens * nh, ATT_WARPS);
   HB_REQUIRE(blocks < 2147483647LL, "attention: too many (token, head) pairs");
   if (dtype == HB_F32)

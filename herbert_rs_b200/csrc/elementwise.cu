@@ -15,7 +15,8 @@
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int hidden, int vocab, float scale) {
+                             float* __restrict__ out, int hidden, int vocab, float scale,
+                             const T* __restrict__ pos_table, const int* __restrict__ positions, int n_positions) {
   pdl_wait();
   pdl_launch();
   const int t = blockIdx.x;
@@ -26,23 +27,37 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     return;
   }
   const T* row = table + (size_t)id * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
+  // a learned vector per position joins the row unscaled; a position beyond the table (the host
+  // refuses such a sequence) adds nothing
+  const T* prow = nullptr;
+  if (pos_table != nullptr) {
+    const int p = positions[t];
+    if (p >= 0 && p < n_positions) prow = pos_table + (size_t)p * hidden;
+  }
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = to_f32(row[i]) * scale;
+    if (prow) v += to_f32(prow[i]);
+    o[i] = v;
+  }
 }
 
 template <typename T>
 static int embed_launch(const void* table, const int* ids, float* out, int n_tokens, int hidden,
-                        int vocab, float scale, void* stream) {
+                        int vocab, float scale, const void* pos_table, const int* positions, int n_positions, void* stream) {
   HB_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: sizes must be positive");
+  HB_REQUIRE(pos_table == nullptr || (positions != nullptr && n_positions > 0), "embed: a position table needs positions");
   int threads = hidden >= 1024 ? 256 : 128;
-  hb_launch(embed_kernel<T>, dim3(n_tokens), dim3(threads), 0, (cudaStream_t)stream, (const T*)table, ids, out, hidden, vocab, scale);
+  hb_launch(embed_kernel<T>, dim3(n_tokens), dim3(threads), 0, (cudaStream_t)stream, (const T*)table, ids, out, hidden, vocab, scale,
+            (const T*)pos_table, positions, n_positions);
   HB_CHECK_LAUNCH("embed");
   return 0;
 }
 
 extern "C" int hb_embed(int dtype, const void* table, const int* ids, float* out, int n_tokens,
-                        int hidden, int vocab, float scale, void* stream) {
-  return dtype == HB_F32 ? embed_launch<float>(table, ids, out, n_tokens, hidden, vocab, scale, stream)
-                         : embed_launch<bf16>(table, ids, out, n_tokens, hidden, vocab, scale, stream);
+                        int hidden, int vocab, float scale, const void* pos_table, const int* positions,
+                        int n_positions, void* stream) {
+  return dtype == HB_F32 ? embed_launch<float>(table, ids, out, n_tokens, hidden, vocab, scale, pos_table, positions, n_positions, stream)
+                         : embed_launch<bf16>(table, ids, out, n_tokens, hidden, vocab, scale, pos_table, positions, n_positions, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

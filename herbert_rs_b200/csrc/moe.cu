@@ -3,6 +3,12 @@
 //   z = R h (float);  s = softmax(z) over all E experts;  the `top` largest s are chosen
 //   weights: the chosen s themselves, or (renorm) divided by their sum
 //   y = sum over the chosen e of weight_e * Down_e act(Up_e h)      act: gelu (erf form) or silu
+// Options of the router: s = sigmoid(z) instead of the softmax; the experts as `groups` equal groups
+// of neighbours, a group's score being the sum of its `group_top` largest s, with only the experts of
+// the `keep` best groups open to the choice (ties between groups, as between experts, go to the
+// lower index); a factor on every weight.  Option of the experts: a gated form
+// Down_e (act(Gate_e h) * (Up_e h)), with the rows of Gate_e and Up_e stored in turn (row 2f: gate f,
+// row 2f + 1: up f) so that one thread of a tile holds both halves of a channel.
 //
 // Three launches, all reading the choice from device memory (nothing of it is known to the host, so
 // a recorded step can be replayed): the router with softmax and choice; the chosen experts' first
@@ -53,17 +59,19 @@ __device__ __forceinline__ float warp_dot(const bf16* a, const bf16* w, int n, i
 }
 
 // One block per token: its warps share the experts' dot products, the first warp then takes the
-// softmax and the choice.
+// scores, the groups and the choice.
 template <typename T>
 __global__ void __launch_bounds__(MOE_ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ h, int ld, const T* __restrict__ wr, int* __restrict__ ids, float* __restrict__ wts,
-                 int n_tokens, int D, int E, int top, int renorm) {
-  extern __shared__ float sh[];  // [E]
+                 int n_tokens, int D, int E, int top, int renorm, int sigmoid, int groups, int keep, int group_top,
+                 float wscale) {
+  extern __shared__ float sh[];  // [E] scores, [groups] group scores
   pdl_wait();
   pdl_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   float* s = sh;
+  float* gs = sh + E;
   const T* hr = h + (size_t)t * ld;
   for (int e = warp; e < E; e += MOE_ROUTE_WARPS) {
     const float dot = warp_dot(hr, wr + (size_t)e * D, D, lane);
@@ -71,14 +79,41 @@ moe_route_kernel(const T* __restrict__ h, int ld, const T* __restrict__ wr, int*
   }
   __syncthreads();
   if (warp != 0) return;
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
-  mx = warp_max(mx);
-  float sum = 0.0f;
-  for (int e = lane; e < E; e += 32) sum += expf(s[e] - mx);
-  sum = warp_sum(sum);
-  for (int e = lane; e < E; e += 32) s[e] = expf(s[e] - mx) / sum;
+  if (sigmoid) {
+    for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
+  } else {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+    mx = warp_max(mx);
+    float sum = 0.0f;
+    for (int e = lane; e < E; e += 32) sum += expf(s[e] - mx);
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) s[e] = expf(s[e] - mx) / sum;
+  }
   __syncwarp();
+  if (groups > 1) {
+    const int size = E / groups;
+    // a group's score: the sum of those of its scores that fewer than group_top others beat
+    for (int g = lane; g < groups; g += 32) {
+      const float* sg = s + g * size;
+      float acc = 0.0f;
+      for (int i = 0; i < size; ++i) {
+        int beaten = 0;
+        for (int j = 0; j < size; ++j) beaten += (sg[j] > sg[i] || (sg[j] == sg[i] && j < i)) ? 1 : 0;
+        if (beaten < group_top) acc += sg[i];
+      }
+      gs[g] = acc;
+    }
+    __syncwarp();
+    // experts of groups that `keep` or more others beat leave the choice (scores are >= 0; -3 never wins)
+    for (int e = lane; e < E; e += 32) {
+      const int g = e / size;
+      int beaten = 0;
+      for (int j = 0; j < groups; ++j) beaten += (gs[j] > gs[g] || (gs[j] == gs[g] && j < g)) ? 1 : 0;
+      if (beaten >= keep) s[e] = -3.0f;
+    }
+    __syncwarp();
+  }
   float chosen_sum = 0.0f;
   for (int r = 0; r < top; ++r) {
     float best = -1.0f;
@@ -93,7 +128,7 @@ moe_route_kernel(const T* __restrict__ h, int ld, const T* __restrict__ wr, int*
     }
     if (lane == 0) {
       ids[(size_t)t * top + r] = bi;
-      wts[(size_t)t * top + r] = best;
+      wts[(size_t)t * top + r] = best * wscale;
       s[bi] = -2.0f;  // taken
     }
     chosen_sum += best;
@@ -104,15 +139,19 @@ moe_route_kernel(const T* __restrict__ h, int ld, const T* __restrict__ wr, int*
 }
 
 extern "C" int hb_moe_route(int dtype, const void* h, int ld, const void* w_router, int* ids, float* weights, int n_tokens,
-                            int D, int E, int top, int renorm, void* stream) {
+                            int D, int E, int top, int renorm, int sigmoid, int groups, int keep, int group_top,
+                            float wscale, void* stream) {
   HB_REQUIRE(n_tokens > 0 && D > 0 && E > 0 && top > 0 && top <= E, "moe_route: bad sizes (experts %d, top %d)", E, top);
-  const size_t smem = (size_t)E * sizeof(float);
+  HB_REQUIRE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups && group_top >= 1,
+             "moe_route: %d experts in %d groups of which %d are kept", E, groups, keep);
+  HB_REQUIRE(top <= (E / groups) * keep, "moe_route: %d groups of %d experts cannot give %d choices", keep, E / groups, top);
+  const size_t smem = (size_t)(E + groups) * sizeof(float);
   HB_REQUIRE(smem <= 48 * 1024, "moe_route: %d experts exceed what a block keeps in shared memory", E);
   dim3 grid(n_tokens);
   if (dtype == HB_F32)
-    hb_launch(moe_route_kernel<float>, grid, dim3(MOE_ROUTE_WARPS * 32), smem, (cudaStream_t)stream, (const float*)h, ld, (const float*)w_router, ids, weights, n_tokens, D, E, top, renorm);
+    hb_launch(moe_route_kernel<float>, grid, dim3(MOE_ROUTE_WARPS * 32), smem, (cudaStream_t)stream, (const float*)h, ld, (const float*)w_router, ids, weights, n_tokens, D, E, top, renorm, sigmoid, groups, keep, group_top, wscale);
   else
-    hb_launch(moe_route_kernel<bf16>, grid, dim3(MOE_ROUTE_WARPS * 32), smem, (cudaStream_t)stream, (const bf16*)h, ld, (const bf16*)w_router, ids, weights, n_tokens, D, E, top, renorm);
+    hb_launch(moe_route_kernel<bf16>, grid, dim3(MOE_ROUTE_WARPS * 32), smem, (cudaStream_t)stream, (const bf16*)h, ld, (const bf16*)w_router, ids, weights, n_tokens, D, E, top, renorm, sigmoid, groups, keep, group_top, wscale);
   HB_CHECK_LAUNCH("moe_route");
   return 0;
 }
@@ -123,19 +162,26 @@ __device__ __forceinline__ float moe_act(float z, int act) {
   return z / (1.0f + expf(-z));
 }
 
-// mid[(t*top + r), f] = act(Up_e[f, :] . h[t, :]),  e = ids[t, r].  One warp per output.
+// mid[(t*top + r), f] = act(Up_e[f, :] . h[t, :]),  e = ids[t, r]; gated: act(row 2f . h) * (row 2f + 1 . h) of
+// the expert's 2F rows.  One warp per output.
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_up_kernel(const T* __restrict__ h, int ld, const T* __restrict__ up, const int* __restrict__ ids, T* __restrict__ mid,
-              int D, int F, int top, int act) {
+              int D, int F, int top, int act, int gated) {
   pdl_wait();
   pdl_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f = blockIdx.y * MOE_WARPS + warp, u = blockIdx.x;  // u = t*top + r
   if (f >= F) return;
   const int e = ids[u];
-  const T* w = up + ((size_t)e * F + f) * D;
   const T* hr = h + (size_t)(u / top) * ld;
+  if (gated) {
+    const T* w = up + ((size_t)e * 2 * F + 2 * f) * D;
+    const float g = warp_dot(hr, w, D, lane), v = warp_dot(hr, w + D, D, lane);
+    if (lane == 0) mid[(size_t)u * F + f] = from_f32<T>(moe_act(g, act) * v);
+    return;
+  }
+  const T* w = up + ((size_t)e * F + f) * D;
   const float dot = warp_dot(hr, w, D, lane);
   if (lane == 0) mid[(size_t)u * F + f] = from_f32<T>(moe_act(dot, act));
 }
@@ -165,17 +211,17 @@ moe_down_kernel(const T* __restrict__ mid, const T* __restrict__ down, const int
 
 extern "C" int hb_moe_experts(int dtype, const void* h, int ld, const void* up, const void* down, const int* ids,
                               const float* weights, void* mid, float* y, int ldy, int n_tokens, int D, int F, int top,
-                              int act, int accumulate, void* stream) {
+                              int act, int gated, int accumulate, void* stream) {
   HB_REQUIRE(n_tokens > 0 && D > 0 && F > 0 && top > 0, "moe_experts: sizes must be positive");
   HB_REQUIRE((long long)n_tokens * top < 2147483647LL && ceil_div(F, MOE_WARPS) <= 65535 && ceil_div(D, MOE_WARPS) <= 65535,
              "moe_experts: too many (token, choice) pairs or channels");
   cudaStream_t s = (cudaStream_t)stream;
   dim3 g1(n_tokens * top, ceil_div(F, MOE_WARPS)), g2(n_tokens, ceil_div(D, MOE_WARPS));
   if (dtype == HB_F32) {
-    hb_launch(moe_up_kernel<float>, g1, dim3(MOE_WARPS * 32), 0, s, (const float*)h, ld, (const float*)up, ids, (float*)mid, D, F, top, act);
+    hb_launch(moe_up_kernel<float>, g1, dim3(MOE_WARPS * 32), 0, s, (const float*)h, ld, (const float*)up, ids, (float*)mid, D, F, top, act, gated);
     hb_launch(moe_down_kernel<float>, g2, dim3(MOE_WARPS * 32), 0, s, (const float*)mid, (const float*)down, ids, weights, y, ldy, D, F, top, accumulate);
   } else {
-    hb_launch(moe_up_kernel<bf16>, g1, dim3(MOE_WARPS * 32), 0, s, (const bf16*)h, ld, (const bf16*)up, ids, (bf16*)mid, D, F, top, act);
+    hb_launch(moe_up_kernel<bf16>, g1, dim3(MOE_WARPS * 32), 0, s, (const bf16*)h, ld, (const bf16*)up, ids, (bf16*)mid, D, F, top, act, gated);
     hb_launch(moe_down_kernel<bf16>, g2, dim3(MOE_WARPS * 32), 0, s, (const bf16*)mid, (const bf16*)down, ids, weights, y, ldy, D, F, top, accumulate);
   }
   HB_CHECK_LAUNCH("moe_experts");
@@ -234,11 +280,12 @@ moe_group_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restric
 
 // C[pair, n] = sum_k A[row(pair), k] * W[e][n][k] for the pairs of tile blockIdx.x of its expert.
 // UP: row(pair) = pair / top of h, C = act(.) as bfloat16 into mid[pair]; else row(pair) = pair of mid, C float into part[pair].
+// UP and gated: W has 2F rows per expert, gate and up in turn, and C[pair, n / 2] = act(even column) * (odd column).
 template <bool UP>
 __global__ void __launch_bounds__(MG_THREADS)
 moe_grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, void* __restrict__ C, int ldc,
                         const int* __restrict__ pair_off, const int* __restrict__ tile_off, const int* __restrict__ list, int E,
-                        int N, int K, int top, int act) {
+                        int N, int K, int top, int act, int gated) {
   __shared__ __align__(16) bf16 AW[2][(MG_TM + MG_TN) * (MG_TK + 8)];      // per buffer: the A tile, then the W tile
   __shared__ int rows[MG_TM];
   pdl_wait();
@@ -329,6 +376,16 @@ moe_grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restr
     for (int half = 0; half < 2; ++half) {
       const int pair = rows[wm + m * 16 + g + half * 8];
       if (pair < 0) continue;
+      if (UP && gated) {
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          const int n = n0 + wn + nt * 8 + 2 * t;      // even: the gate's column; N is even, so n + 1 < N too
+          if (n >= N) continue;
+          ((bf16*)C)[(size_t)pair * ldc + (n >> 1)] =
+              __float2bfloat16_rn(moe_act(acc[m][nt][half * 2], act) * acc[m][nt][half * 2 + 1]);
+        }
+        continue;
+      }
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
@@ -361,8 +418,8 @@ extern "C" long long hb_moe_grouped_scratch_ints(int n_tokens, int E, int top) {
 // scratch: hb_moe_grouped_scratch_ints ints; mid [T * top, F] bfloat16; part [T * top, D] floats.
 extern "C" int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up, const void* down, const int* ids,
                                            const float* weights, int* scratch, void* mid, float* part, float* y, int ldy,
-                                           int n_tokens, int D, int E, int F, int top, int act, int accumulate,
-                                           void* stream) {
+                                           int n_tokens, int D, int E, int F, int top, int act, int gated,
+                                           int accumulate, void* stream) {
   HB_REQUIRE(n_tokens > 0 && D > 0 && E > 0 && F > 0 && top > 0, "moe_experts_grouped: sizes must be positive");
   HB_REQUIRE(E <= MG_MAX_EXPERTS, "moe_experts_grouped: at most %d experts", MG_MAX_EXPERTS);
   HB_REQUIRE(D % 8 == 0 && F % 8 == 0 && ld % 8 == 0, "moe_experts_grouped: widths must be multiples of 8");
@@ -374,10 +431,11 @@ extern "C" int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up
   cudaStream_t s = (cudaStream_t)stream;
   hb_launch(moe_group_kernel, dim3(1), dim3(1024), 0, s, ids, n_pairs, E, pair_off, tile_off, list);
   const int max_tiles = ceil_div(n_pairs, MG_TM) + E;
-  hb_launch(moe_grouped_gemm_kernel<true>, dim3(max_tiles, ceil_div(F, MG_TN)), dim3(MG_THREADS), 0, s, (const bf16*)h, ld, (const bf16*)up,
-            mid, F, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, F, D, top, act);
+  const int n_up = gated ? 2 * F : F;      // rows of an expert's first matrix
+  hb_launch(moe_grouped_gemm_kernel<true>, dim3(max_tiles, ceil_div(n_up, MG_TN)), dim3(MG_THREADS), 0, s, (const bf16*)h, ld, (const bf16*)up,
+            mid, F, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, n_up, D, top, act, gated);
   hb_launch(moe_grouped_gemm_kernel<false>, dim3(max_tiles, ceil_div(D, MG_TN)), dim3(MG_THREADS), 0, s, (const bf16*)mid, F,
-            (const bf16*)down, (void*)part, D, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, D, F, top, act);
+            (const bf16*)down, (void*)part, D, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, D, F, top, act, 0);
   hb_launch(moe_combine_kernel, dim3(ceil_div(D, 256), n_tokens), dim3(256), 0, s, (const float*)part, weights, y, ldy, D, top, accumulate);
   HB_CHECK_LAUNCH("moe_experts_grouped");
   return 0;

@@ -2,6 +2,7 @@
 
 from ..config.kebisun import KebisunConfig
 from ..config.qwen3 import Qwen3Config
+from ..config.votapel import VotapelConfig
 from ..registry import register_architecture
 from .decoder import DecoderModel
 
@@ -10,5 +11,8 @@ register_architecture("Qwen3ForCausalLM", Qwen3Config, model_types=("qwen3",), d
 # Layers of two mixer kinds (latent attention, gated linear attention) with dense or routed
 # feed-forwards; config.json names it under "architecture".
 register_architecture("Kebisun", KebisunConfig)
+# Parallel blocks (one norm, attention and a routed feed-forward side by side) of attention whose values
+# are its keys, with biases, a query temperature, capped scores and a sink; learned position vectors.
+register_architecture("Votapel", VotapelConfig)
 
 __all__ = ["DecoderModel"]

@@ -31,6 +31,7 @@ class DecoderModel:
         self.final_norm = build_part("norm", spec.final_norm, rt=rt)
         self.embed = None
         self.head = None
+        self.position_table = None      # [max_position, hidden] learned vectors, if the spec names one
         for i, st in enumerate(spec.schedule):
             if not (0 <= st.layer < len(self.blocks)):
                 raise ConfigError(f"schedule step {i} names layer {st.layer}, but there are {len(self.blocks)} layers")
@@ -42,6 +43,8 @@ class DecoderModel:
     def param_specs(self) -> Dict[str, ParamSpec]:
         s = self.spec
         out = {s.embed_name: ParamSpec((s.vocab_size, s.hidden_size))}
+        if s.position_table_name:
+            out[s.position_table_name] = ParamSpec((s.max_position, s.hidden_size))
         for i, b in enumerate(self.blocks):
             for name, ps in b.param_specs().items():
                 out[self.block_prefix(i) + name] = ps
@@ -64,6 +67,9 @@ class DecoderModel:
         if self.spec.tie_word_embeddings:
             self.head = self.embed  # one buffer, two uses (loader_common.rs:1851-1860)
 
+    def load_position_table(self, t: torch.Tensor) -> None:
+        self.position_table = t.contiguous()
+
     def load_head(self, t: torch.Tensor) -> None:
         self.head = t.contiguous()
 
@@ -75,7 +81,7 @@ class DecoderModel:
         of the embedding only the gathered rows."""
         n = sum(self.blocks[st.layer].weight_bytes() for st in self.spec.schedule)
         n += self.final_norm.weight_bytes() + self.head.numel() * self.head.element_size()
-        n += rows * self.spec.hidden_size * self.embed.element_size()
+        n += rows * self.spec.hidden_size * self.embed.element_size() * (2 if self.position_table is not None else 1)
         return n
 
     @property
@@ -97,7 +103,7 @@ class DecoderModel:
         ws = self.rt.workspace
         ws.rewind()
         x = ws.take((batch.n_tokens, self.spec.hidden_size), torch.float32)
-        ops.embed(self.embed, batch.token_ids, x, self.spec.embedding_scale)
+        ops.embed(self.embed, batch.token_ids, x, self.spec.embedding_scale, self.position_table, batch.tok_pos)
         # a block may begin the first norm of the block that runs after it (parts/base.py)
         sched, pending = self.spec.schedule, None
         for i, st in enumerate(sched):

@@ -27,7 +27,10 @@ SKINNY_MAX_ROWS = 64
 options = KernelOptions()
 
 _SIGS = {
-    "hb_embed": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+    "hb_embed": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p],
+    "hb_scaled_residual_norm": [c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    "hb_qk_prepare_cache": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p,
+                            c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_rmsnorm": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     "hb_swiglu": [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_add_residual": [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -51,7 +54,7 @@ _SIGS = {
     "hb_gemm_stream_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                             ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p],
     "hb_attention_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p],
     "hb_attention_decode_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_decode_fused_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
@@ -79,7 +82,7 @@ _SIGS = {
     "hb_latent_attention": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_moe_experts_grouped_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_latent_attention_mma_ok": [c_int, c_int],
     "hb_latent_attention_mma_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
@@ -88,9 +91,10 @@ _SIGS = {
                     c_int, c_int, c_int, c_float, c_void_p],
     "hb_gla_output": [c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                       c_void_p],
-    "hb_moe_route": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_moe_route": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                     c_int, c_int, c_float, c_void_p],
     "hb_moe_experts": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                       c_int, c_int, c_int, c_int, c_int, c_void_p],
+                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
 }
 _fns: dict = {}
 
@@ -290,11 +294,44 @@ def cast(src: torch.Tensor, dtype: torch.dtype, round_bf16: bool = False) -> tor
     return out
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
-    """out[t, :] = float(table[ids[t], :]) * scale; out is the float residual stream [T, H]."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0,
+          pos_table: torch.Tensor | None = None, positions: torch.Tensor | None = None) -> None:
+    """out[t, :] = float(table[ids[t], :]) * scale (+ float(pos_table[positions[t], :]) with a table of
+    learned position vectors, in the embedding's dtype); out is the float residual stream [T, H]."""
     _check(table, None, "table"); _check(ids, torch.int32, "ids"); _check(out, torch.float32, "out")
+    if pos_table is not None:
+        _check(pos_table, table.dtype, "pos_table"); _check(positions, torch.int32, "positions")
+        if pos_table.shape[1] != table.shape[1] or not pos_table.is_contiguous():
+            raise BackendError("embed: the position table must be contiguous and as wide as the embedding")
     _run("hb_embed", dtype_code(table.dtype), table.data_ptr(), ids.data_ptr(), out.data_ptr(),
-         ids.numel(), table.shape[1], table.shape[0], float(scale), _stream())
+         ids.numel(), table.shape[1], table.shape[0], float(scale), _ptr(pos_table),
+         _ptr(positions) if pos_table is not None else None, 0 if pos_table is None else pos_table.shape[0], _stream())
+
+
+def scaled_residual_norm(y: torch.Tensor, mult: float, x: torch.Tensor, w: torch.Tensor | None = None,
+                         h: torch.Tensor | None = None, eps: float = 0.0) -> None:
+    """x += mult * y (float); with w and h: h = x / sqrt(mean(x^2) + eps) * w of the updated rows, in h's dtype."""
+    _check(y, torch.float32, "y"); _check(x, torch.float32, "x")
+    if not x.is_contiguous() or (h is not None and not h.is_contiguous()):
+        raise BackendError("scaled_residual_norm: x and h must be contiguous")
+    if w is not None:
+        _check(w, torch.float32, "w"); _check(h, None, "h")
+    _run("hb_scaled_residual_norm", dtype_code(h.dtype) if h is not None else F32, y.data_ptr(), y.stride(0), float(mult),
+         x.data_ptr(), _ptr(w), _ptr(h), x.shape[0], x.shape[1], float(eps), _stream())
+
+
+def qk_prepare_cache(rows, bias, q_out, temp_coef, temp_every, tok_seq, tok_pos, seq_pages, k_cache, v_cache, num_heads,
+                     num_kv_heads, head_dim, page_size, write_cache=True) -> None:
+    """Float rows [q heads | k heads (| v heads)] of a projection: biases added (bias in the row's layout, or
+    None), q times 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) (temp_every 0: no temperature) into
+    q_out, k (and v, if a value plane is given) into the paged cache at the token's place."""
+    _check(rows, torch.float32, "rows"); _check(q_out, k_cache.dtype, "q_out")
+    if bias is not None:
+        _check(bias, torch.float32, "bias")
+    _run("hb_qk_prepare_cache", dtype_code(q_out.dtype), rows.data_ptr(), rows.stride(0), _ptr(bias), q_out.data_ptr(),
+         q_out.stride(0), float(temp_coef), int(temp_every), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_pages.data_ptr(),
+         seq_pages.stride(0), k_cache.data_ptr(), _ptr(v_cache), rows.shape[0], int(num_heads), int(num_kv_heads),
+         int(head_dim), int(page_size), 1 if write_cache else 0, _stream())
 
 
 def to_activation(x: torch.Tensor, out: torch.Tensor) -> None:
@@ -418,12 +455,16 @@ def gla_output(o, w, eps, gate, out, heads, dv) -> None:
          gate.stride(0), out.data_ptr(), out.stride(0), o.shape[0], int(heads), int(dv), _stream())
 
 
-def moe_route(h, w_router, ids, weights, top, renorm=False) -> None:
-    """ids[t, :top], weights[t, :top]: the `top` largest of softmax(w_router h[t]) over all experts (ties to
-    the lower index), the weights being those softmax values (divided by their sum with `renorm`)."""
+def moe_route(h, w_router, ids, weights, top, renorm=False, score=0, groups=1, keep=1, group_top=2, weight_scale=1.0) -> None:
+    """ids[t, :top], weights[t, :top]: the `top` largest scores of w_router h[t] (ties to the lower index);
+    score 0: softmax over all experts, 1: sigmoid.  With groups > 1 the experts form that many equal groups of
+    neighbours, a group's score is the sum of its `group_top` largest scores, and only the experts of the
+    `keep` best groups can be chosen.  The weights are the chosen scores (divided by their sum with `renorm`)
+    times `weight_scale`."""
     _check(h, None, "h"); _check(w_router, h.dtype, "w_router"); _check(ids, torch.int32, "ids"); _check(weights, torch.float32, "weights")
     _run("hb_moe_route", dtype_code(h.dtype), h.data_ptr(), h.stride(0), w_router.data_ptr(), ids.data_ptr(), weights.data_ptr(),
-         h.shape[0], h.shape[1], w_router.shape[0], int(top), 1 if renorm else 0, _stream())
+         h.shape[0], h.shape[1], w_router.shape[0], int(top), 1 if renorm else 0, int(score), int(groups), int(keep),
+         int(group_top), float(weight_scale), _stream())
 
 
 MOE_GROUPED_MIN_TOKENS = 32
@@ -437,28 +478,31 @@ def moe_grouped_ok(h, up) -> bool:
             and D % 8 == 0 and F % 8 == 0 and h.stride(0) % 8 == 0 and E <= 1024 and h.data_ptr() % 16 == 0)
 
 
-def moe_experts_grouped(h, up, down, ids, weights, y, act, accumulate, scratch) -> None:
+def moe_experts_grouped(h, up, down, ids, weights, y, act, accumulate, scratch, gated=False) -> None:
     """moe_experts for many tokens: pairs grouped by expert on the device, tiles of 64 pairs on the tensor cores."""
     _check(h, torch.bfloat16, "h"); _check(up, torch.bfloat16, "up"); _check(down, torch.bfloat16, "down"); _check(y, torch.float32, "y")
     T, top = ids.shape
     E, F, D = up.shape
+    if gated:
+        F //= 2
     ints = scratch((2 * (E + 1) + T * top,), torch.int32)
     mid = scratch((T * top, F), torch.bfloat16)
     part = scratch((T * top, D), torch.float32)
     _run("hb_moe_experts_grouped_bf16", h.data_ptr(), h.stride(0), up.data_ptr(), down.data_ptr(), ids.data_ptr(), weights.data_ptr(),
          ints.data_ptr(), mid.data_ptr(), part.data_ptr(), y.data_ptr(), y.stride(0), T, D, E, F, top, int(act),
-         1 if accumulate else 0, _stream())
+         1 if gated else 0, 1 if accumulate else 0, _stream())
 
 
-def moe_experts(h, up, down, ids, weights, mid, y, act, accumulate=False) -> None:
+def moe_experts(h, up, down, ids, weights, mid, y, act, accumulate=False, gated=False) -> None:
     """y[t] (+)= sum_r weights[t, r] * down[e] act(up[e] h[t]), e = ids[t, r]; up [E, F, D], down [E, D, F] in
-    h's dtype; mid [T * top, F] scratch in h's dtype; y float."""
+    h's dtype; mid [T * top, F] scratch in h's dtype; y float.  gated: up is [E, 2F, D] with gate and up rows in
+    turn and an expert is down[e] (act(gate h) * (up h))."""
     _check(h, None, "h"); _check(up, h.dtype, "up"); _check(down, h.dtype, "down"); _check(mid, h.dtype, "mid"); _check(y, torch.float32, "y")
     if not (up.is_contiguous() and down.is_contiguous() and mid.is_contiguous()):
         raise BackendError("moe_experts: up, down and mid must be contiguous")
     _run("hb_moe_experts", dtype_code(h.dtype), h.data_ptr(), h.stride(0), up.data_ptr(), down.data_ptr(), ids.data_ptr(),
-         weights.data_ptr(), mid.data_ptr(), y.data_ptr(), y.stride(0), h.shape[0], h.shape[1], up.shape[1], ids.shape[1],
-         int(act), 1 if accumulate else 0, _stream())
+         weights.data_ptr(), mid.data_ptr(), y.data_ptr(), y.stride(0), h.shape[0], h.shape[1], down.shape[2], ids.shape[1],
+         int(act), 1 if gated else 0, 1 if accumulate else 0, _stream())
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
@@ -502,11 +546,15 @@ def gemm_simt(a, w, c, epilogue=EPI_STORE) -> None:
 
 
 def attention_simt(q, ldq, out, k_cache, v_cache, tok_seq, tok_pos, seq_pages, num_heads, num_kv_heads,
-                   head_dim, page_size, scale, window) -> None:
+                   head_dim, page_size, scale, window, softcap=None, sink=None) -> None:
+    """Any shape, both precisions.  softcap c: score <- c * tanh(score / c); sink [num_heads] float: exp(sink)
+    joins each head's softmax denominator.  v_cache may be k_cache (values that are the keys)."""
+    if sink is not None:
+        _check(sink, torch.float32, "sink")
     _run("hb_attention_simt", dtype_code(out.dtype), q.data_ptr(), int(ldq), out.data_ptr(), out.stride(0),
          k_cache.data_ptr(), v_cache.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_pages.data_ptr(),
          seq_pages.stride(0), out.shape[0], num_heads, num_kv_heads, head_dim, page_size, float(scale),
-         int(window or 0), _stream())
+         int(window or 0), float(softcap or 0.0), _ptr(sink), _stream())
 
 
 _argmax_scratch: dict = {}
@@ -952,12 +1000,16 @@ def _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size) -> bool
 
 
 def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, head_dim, page_size,
-              scale, window, seq_pages, scratch=None) -> None:
+              scale, window, seq_pages, scratch=None, softcap=None, sink=None) -> None:
     """Attention of every token of the step over its sequence's cached keys and values.
 
     bfloat16 steps of one token per sequence take the split-key tensor-core kernel, other bfloat16
     steps the flash kernel; head sizes or pages those cannot serve, and the float32 path, take
     the any-shape kernel."""
+    if softcap or sink is not None:
+        attention_simt(q, ldq, out, k_cache, v_cache, batch.tok_seq, batch.tok_pos, seq_pages, num_heads,
+                       num_kv_heads, head_dim, page_size, scale, window, softcap, sink)
+        return
     if batch.is_decode and scratch is not None and _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size):
         tiles = seq_pages.shape[1] * (page_size // 64)
         nsplit = decode_splits(batch.n_seqs, num_kv_heads, tiles)
@@ -974,4 +1026,4 @@ def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, hea
                           batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window)
         return
     attention_simt(q, ldq, out, k_cache, v_cache, batch.tok_seq, batch.tok_pos, seq_pages, num_heads,
-                   num_kv_heads, head_dim, page_size, scale, window)
+                   num_kv_heads, head_dim, page_size, scale, window, softcap, sink)

@@ -8,9 +8,9 @@ from .latent_attention import LatentAttentionMixer
 from .gla import GatedLinearAttentionMixer
 from .swiglu import SwiGLU, join_gate_up
 from .moe import RoutedFeedForward
-from .block import PreNormBlock, SublayerNormBlock
+from .block import ParallelBlock, PreNormBlock, SublayerNormBlock
 
 __all__ = ["Block", "FeedForward", "Mixer", "Norm", "ParamSpec", "Part", "RMSNorm", "RotaryEncoding",
            "rope_tables", "AttentionMixer", "SwiGLU", "join_gate_up", "PreNormBlock", "LayerNorm", "ScaledRotary",
            "scaled_frequencies", "LatentAttentionMixer", "GatedLinearAttentionMixer", "RoutedFeedForward",
-           "SublayerNormBlock"]
+           "SublayerNormBlock", "ParallelBlock"]

@@ -9,6 +9,13 @@ its own position; result times o_proj, added to the residual stream.
 
 The three projections are one matrix here (rows of q, then k, then v), joined at load time, so
 one product yields the row layout the fused norm/rotation/cache kernel reads.
+
+Options of the spec that other designs use (`AttentionSpec`): biases on the projections, values
+that are the keys themselves (no value product, a cache of one plane), a query temperature that
+grows with the position, a cap on the scores, a sink in the softmax's denominator.  A mixer with
+any of these takes the second path below: the product leaves float rows, one kernel adds the
+biases, applies the temperature and writes q and the cache (each number rounded once), and the
+attention kernels take the cap and the sink as parameters.
 """
 
 from __future__ import annotations
@@ -17,6 +24,7 @@ import torch
 
 from .. import ops
 from ..cache import CacheNeed, KVNeed
+from ..errors import ConfigError
 from ..registry import build_part, register_part
 from .base import Mixer, ParamSpec
 
@@ -28,25 +36,52 @@ class AttentionMixer(Mixer):
         self.q_dim, self.kv_dim = self.nh * self.hd, self.nkv * self.hd
         self.qkv_dim = self.q_dim + 2 * self.kv_dim
         self.position = build_part("position", spec.position, rt=rt) if spec.position is not None else None
-        self.wqkv = self.wo = self.q_norm = self.k_norm = None
+        self.wqkv = self.wo = self.q_norm = self.k_norm = self.bias = self.sink = None
+        self.n_q, self.n_k, self.n_v, self.n_o, self.n_sink = spec.names
+        self.shared_values = bool(spec.values_are_keys)
+        # the plain form (no option set) keeps the path with the fused kernels of the dense decoder
+        self.plain = not (spec.bias or spec.values_are_keys or spec.q_temperature or spec.softcap or spec.sink)
+        if not self.plain and (spec.qk_norm is not None or spec.position is not None):
+            raise ConfigError("attention with biases, shared values, a query temperature, a cap or a sink has no "
+                              "head norm and no rotation here")
+        self.shares_norms = self.plain
+        self.can_store = not self.plain
+        if not self.shared_values:
+            self.qkv_dim = self.q_dim + 2 * self.kv_dim
+        else:
+            self.qkv_dim = self.q_dim + self.kv_dim
+
+    def _matrices(self):
+        return [self.n_q, self.n_k] + ([] if self.shared_values else [self.n_v])
 
     def param_specs(self):
         s = self.spec
         p = {
-            "q_proj.weight": ParamSpec((self.q_dim, s.hidden_size)),
-            "k_proj.weight": ParamSpec((self.kv_dim, s.hidden_size)),
-            "v_proj.weight": ParamSpec((self.kv_dim, s.hidden_size)),
-            "o_proj.weight": ParamSpec((s.hidden_size, self.q_dim)),
+            self.n_q: ParamSpec((self.q_dim, s.hidden_size)),
+            self.n_k: ParamSpec((self.kv_dim, s.hidden_size)),
+            self.n_o: ParamSpec((s.hidden_size, self.q_dim)),
         }
+        if not self.shared_values:
+            p[self.n_v] = ParamSpec((self.kv_dim, s.hidden_size))
+        if s.bias:
+            for n in self._matrices():
+                p[n + s.bias_suffix] = ParamSpec((p[n].shape[0],), role="vector", init="normal")
+        if s.sink:
+            p[self.n_sink] = ParamSpec((self.nh,), role="vector", init="wide")
         if s.qk_norm is not None:
             p["q_norm.weight"] = ParamSpec((self.hd,), role="vector", init="ones_noise")
             p["k_norm.weight"] = ParamSpec((self.hd,), role="vector", init="ones_noise")
         return p
 
     def load(self, tensors):
-        self.wqkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], dim=0).contiguous()
-        self.wo = tensors["o_proj.weight"].contiguous()
-        if self.spec.qk_norm is not None:
+        s = self.spec
+        self.wqkv = torch.cat([tensors[n] for n in self._matrices()], dim=0).contiguous()
+        self.wo = tensors[self.n_o].contiguous()
+        if s.bias:
+            self.bias = torch.cat([tensors[n + s.bias_suffix] for n in self._matrices()], dim=0).contiguous()
+        if s.sink:
+            self.sink = tensors[self.n_sink].contiguous()
+        if s.qk_norm is not None:
             self.q_norm = tensors["q_norm.weight"].contiguous()
             self.k_norm = tensors["k_norm.weight"].contiguous()
 
@@ -54,11 +89,27 @@ class AttentionMixer(Mixer):
         return (self.wqkv.numel() + self.wo.numel()) * self.wqkv.element_size()
 
     def cache_need(self):
-        return CacheNeed(kv=KVNeed(self.nkv, self.hd, self.spec.window))
+        return CacheNeed(kv=KVNeed(self.nkv, self.hd, self.spec.window, planes=1 if self.shared_values else 2))
 
-    shares_norms = True
+    def _forward_options(self, h, residual, batch, cache, accumulate):
+        """The path of a mixer with any of the spec's options (see the module's notes)."""
+        s, ws, T = self.spec, self.rt.workspace, h.shape[0]
+        rows = ws.take((T, self.qkv_dim), torch.float32)
+        ops.gemm(h, self.wqkv, rows, ops.EPI_STORE_F32, scratch=ws.take)
+        q = ws.take((T, self.q_dim), h.dtype)
+        pages = batch.pages[cache.kv_group]
+        coef, every = s.q_temperature if s.q_temperature else (0.0, 0)
+        ops.qk_prepare_cache(rows, self.bias, q, coef, every, batch.tok_seq, batch.tok_pos, pages, cache.k,
+                             None if self.shared_values else cache.v, self.nh, self.nkv, self.hd, cache.page_size,
+                             write_cache=cache.writes_kv)
+        att = ws.take((T, self.q_dim), h.dtype)
+        ops.attention(q, q.stride(0), att, cache.k, cache.k if self.shared_values else cache.v, batch, self.nh, self.nkv,
+                      self.hd, cache.page_size, s.scale, s.window, pages, scratch=ws.take, softcap=s.softcap, sink=self.sink)
+        ops.gemm(att, self.wo, residual, ops.EPI_RESIDUAL if accumulate else ops.EPI_STORE_F32, scratch=ws.take)
 
-    def forward(self, h, residual, batch, cache, next_norm=None):
+    def forward(self, h, residual, batch, cache, next_norm=None, accumulate=True):
+        if not self.plain:
+            return self._forward_options(h, residual, batch, cache, accumulate)
         ws, T = self.rt.workspace, h.shape[0]
         qkv = ws.take((T, self.qkv_dim), h.dtype)
         pages = batch.pages[cache.kv_group]

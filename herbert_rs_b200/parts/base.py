@@ -39,7 +39,7 @@ class ParamSpec:
     role "matrix": kept in the compute dtype (bfloat16 as stored; widened exactly on the 32-bit
     path).  role "vector": small per-channel weights, kept in float32 on both paths (a tensor
     stored in 32-bit stays so; a bfloat16 one widens exactly).  role "table": integers, int32.
-    init: "normal" = N(0, 0.02); "ones_noise" = 1 + N(0, 0.1); "wide" = N(0, 1); "zeros".
+    init: "normal" = N(0, 0.02); "ones_noise" = 1 + N(0, 0.1); "zeros_noise" = N(0, 0.1); "wide" = N(0, 1); "zeros".
     A shape entry of -1 is a size that only the stored tensor gives (random weights take `free_size`).
     """
 

@@ -52,6 +52,8 @@ class PreNormBlock(Block):
 
     def _input(self, pending, norm, part, x):
         """What `part` reads: the pending norm itself if it can finish it, else the plain result."""
+        if isinstance(pending, torch.Tensor):
+            return pending              # the block before has already run this norm to its end
         if pending is not None and part.shares_norms:
             return pending
         h = self.rt.workspace.take(x.shape, self.rt.dtype)
@@ -158,5 +160,79 @@ class SublayerNormBlock(Block):
         return None
 
 
+class ParallelBlock(Block):
+    """h = norm1(x); x += m * (mixer(h) + ffn(h)): one norm whose result both sublayers read, one
+    factor m on their sum.  The sublayers write into one float array (the mixer stores, the
+    feed-forward adds), and one kernel adds it, times m, to the stream and runs the RMS norm the next
+    block begins with, so that between two layers the stream is read and written once.  The spec may
+    leave out the feed-forward."""
+
+    chains_norms = True
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.norm1 = build_part("norm", spec.norm1, rt=rt)
+        self.mixer = build_part("mixer", spec.mixer, rt=rt)
+        self.ffn = build_part("ffn", spec.ffn, rt=rt) if spec.ffn is not None else None
+        self.mult = float(spec.residual_mult)
+        self._names = dict(spec.names)
+        for part in (self.mixer, self.ffn):
+            if part is not None and not part.can_store:
+                raise ConfigError(f"{type(part).__name__} cannot store its result apart from the residual stream, "
+                                  "which a block that adds both sublayers at once needs")
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for _, p in self.children())
+
+    def children(self):
+        parts = [("norm1", self.norm1), ("mixer", self.mixer)]
+        if self.ffn is not None:
+            parts.append(("ffn", self.ffn))
+        return tuple(parts)
+
+    def _key(self, local, name):
+        prefix = self._names[local]
+        return f"{prefix}.{name}" if prefix else name
+
+    def param_specs(self):
+        return {self._key(local, name): ps for local, part in self.children() for name, ps in part.param_specs().items()}
+
+    def load(self, tensors):
+        for local, part in self.children():
+            part.load({name: tensors[self._key(local, name)] for name in part.param_specs()})
+
+    def weight_bytes(self):
+        return sum(p.weight_bytes() for _, p in self.children())
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def first_norm(self):
+        return self.norm1
+
+    def forward(self, x, batch, cache, normed=None, next_norm=None):
+        ws, dtype = self.rt.workspace, self.rt.dtype
+        if isinstance(normed, torch.Tensor):
+            h = normed
+        else:
+            h = ws.take(x.shape, dtype)
+            if normed is not None:
+                ops.finish_norm(normed, h)
+            else:
+                self.norm1.forward(x, h)
+        y = ws.take(x.shape, torch.float32)
+        self.mixer.forward(h, y, batch, cache, accumulate=False)
+        if self.ffn is not None:
+            self.ffn.forward(h, y, batch, accumulate=True)
+        if next_norm is None:
+            ops.scaled_residual_norm(y, self.mult, x)
+            return None
+        h_next = ws.take(x.shape, dtype)
+        ops.scaled_residual_norm(y, self.mult, x, next_norm[0], h_next, next_norm[1])
+        return h_next
+
+
+register_part("block", "parallel", ParallelBlock)
 register_part("block", "prenorm", PreNormBlock)
 register_part("block", "sublayer_norm", SublayerNormBlock)

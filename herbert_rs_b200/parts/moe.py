@@ -5,6 +5,11 @@
 
 The experts' matrices are stacked at load time ([E, F, D] and [E, D, F]) so that a kernel finds an
 expert by its index; which experts a token uses never reaches the host, so a recorded step replays.
+
+Options of the spec: sigmoid scores; groups of experts of which only the best stay open to the choice;
+a factor on the weights; gated experts, out_e = Down_e (act(Gate_e h) * (Up_e h)), whose gate and up
+rows are stored in turn in one [E, 2F, D] stack (row 2f: gate f, row 2f + 1: up f); a shared dense
+feed-forward that every token passes and that is added to the experts' sum.
 """
 
 from __future__ import annotations
@@ -13,8 +18,10 @@ import torch
 
 from .. import ops
 from ..errors import ConfigError
-from ..registry import register_part
+from ..registry import build_part, register_part
 from .base import FeedForward, ParamSpec
+
+SCORES = {"softmax": 0, "sigmoid": 1}
 
 
 class RoutedFeedForward(FeedForward):
@@ -25,6 +32,17 @@ class RoutedFeedForward(FeedForward):
         if spec.activation not in ops.ACTIVATIONS:
             raise ConfigError(f"unknown activation {spec.activation!r}: {', '.join(ops.ACTIVATIONS)}")
         self.act = ops.ACTIVATIONS[spec.activation]
+        if spec.score not in SCORES:
+            raise ConfigError(f"unknown router score {spec.score!r}: {', '.join(SCORES)}")
+        if len(spec.expert_names) != (3 if spec.gated else 2):
+            raise ConfigError("a gated expert has three tensors (gate, up, down), a plain one two (up, down)")
+        if spec.groups < 1 or spec.num_experts % spec.groups or not (1 <= spec.keep_groups <= spec.groups):
+            raise ConfigError(f"{spec.num_experts} experts cannot form {spec.groups} equal groups of which {spec.keep_groups} stay")
+        if spec.top_k > spec.keep_groups * (spec.num_experts // spec.groups):
+            raise ConfigError(f"top_k ({spec.top_k}) exceeds the experts of the {spec.keep_groups} kept groups")
+        self.shared = build_part("ffn", spec.shared, rt=rt) if spec.shared is not None else None
+        if self.shared is not None and not self.shared.can_store:
+            raise ConfigError("the shared feed-forward must be able to add into a given array")
 
     def _names(self, e):
         return tuple(n.format(e=e) for n in self.spec.expert_names)
@@ -33,33 +51,47 @@ class RoutedFeedForward(FeedForward):
         s = self.spec
         p = {s.router_name: ParamSpec((s.num_experts, s.hidden_size), init="wide")}
         for e in range(s.num_experts):
-            up, down = self._names(e)
-            p[up] = ParamSpec((s.expert_size, s.hidden_size))
-            p[down] = ParamSpec((s.hidden_size, s.expert_size))
+            names = self._names(e)
+            for n in names[:-1]:
+                p[n] = ParamSpec((s.expert_size, s.hidden_size))
+            p[names[-1]] = ParamSpec((s.hidden_size, s.expert_size))
+        if self.shared is not None:
+            p.update(self.shared.param_specs())
         return p
 
     def load(self, t):
         s = self.spec
         self.router = t[s.router_name].contiguous()
-        self.up = torch.stack([t[self._names(e)[0]] for e in range(s.num_experts)]).contiguous()
-        self.down = torch.stack([t[self._names(e)[1]] for e in range(s.num_experts)]).contiguous()
+        if s.gated:
+            # [E, F, 2, D] -> [E, 2F, D]: gate and up rows in turn
+            self.up = torch.stack([torch.stack([t[self._names(e)[0]], t[self._names(e)[1]]], dim=1)
+                                   for e in range(s.num_experts)]).reshape(s.num_experts, 2 * s.expert_size, s.hidden_size).contiguous()
+        else:
+            self.up = torch.stack([t[self._names(e)[0]] for e in range(s.num_experts)]).contiguous()
+        self.down = torch.stack([t[self._names(e)[-1]] for e in range(s.num_experts)]).contiguous()
+        if self.shared is not None:
+            self.shared.load({n: t[n] for n in self.shared.param_specs()})
 
     def weight_bytes(self):
-        """What a step of one token reads: the router and top_k experts."""
+        """What a step of one token reads: the router, top_k experts and the shared feed-forward."""
         s = self.spec
-        per = 2 * s.expert_size * s.hidden_size * self.up.element_size()
-        return self.router.numel() * self.router.element_size() + s.top_k * per
+        per = (3 if s.gated else 2) * s.expert_size * s.hidden_size * self.up.element_size()
+        shared = self.shared.weight_bytes() if self.shared is not None else 0
+        return self.router.numel() * self.router.element_size() + s.top_k * per + shared
 
     def forward(self, h, residual, batch, accumulate=True):
         s, ws, T = self.spec, self.rt.workspace, h.shape[0]
         ids = ws.take((T, s.top_k), torch.int32)
         weights = ws.take((T, s.top_k), torch.float32)
-        ops.moe_route(h, self.router, ids, weights, s.top_k, s.renormalize)
+        ops.moe_route(h, self.router, ids, weights, s.top_k, s.renormalize, SCORES[s.score], s.groups, s.keep_groups,
+                      s.group_top, s.weight_scale)
         if ops.moe_grouped_ok(h, self.up):
-            ops.moe_experts_grouped(h, self.up, self.down, ids, weights, residual, self.act, accumulate, ws.take)
-            return
-        mid = ws.take((T * s.top_k, s.expert_size), h.dtype)
-        ops.moe_experts(h, self.up, self.down, ids, weights, mid, residual, self.act, accumulate)
+            ops.moe_experts_grouped(h, self.up, self.down, ids, weights, residual, self.act, accumulate, ws.take, gated=s.gated)
+        else:
+            mid = ws.take((T * s.top_k, s.expert_size), h.dtype)
+            ops.moe_experts(h, self.up, self.down, ids, weights, mid, residual, self.act, accumulate, gated=s.gated)
+        if self.shared is not None:
+            self.shared.forward(h, residual, batch, accumulate=True)
 
 
 register_part("ffn", "moe", RoutedFeedForward)

@@ -1,5 +1,7 @@
 """RMSNorm: y = (x / sqrt(mean(x^2) + eps)) * w, in float
-(crates/backends/backend_common/src/kernels.rs:54-64), and the layer norm with a weight and no bias."""
+(crates/backends/backend_common/src/kernels.rs:54-64), and the layer norm with a weight and no bias.
+A spec with `weight_offset` c stores w - c (weights around zero with c = 1); the offset is added once,
+in float, when the tensor is loaded, so every kernel and the norm shared between two products see w."""
 
 from __future__ import annotations
 
@@ -12,13 +14,16 @@ class RMSNorm(Norm):
     def __init__(self, spec, rt):
         self.dim, self.eps, self.rt = spec.dim, spec.eps, rt
         self.name = getattr(spec, "weight_name", "weight")
+        self.offset = float(getattr(spec, "weight_offset", 0.0))
         self.weight = None
 
     def param_specs(self):
-        return {self.name: ParamSpec((self.dim,), role="vector", init="ones_noise")}
+        # random weights lie around 1 - offset: the factor the kernels see is around 1 either way
+        return {self.name: ParamSpec((self.dim,), role="vector", init="ones_noise" if self.offset == 0.0 else "zeros_noise")}
 
     def load(self, tensors):
-        self.weight = tensors[self.name].contiguous()
+        w = tensors[self.name]
+        self.weight = (w + self.offset if self.offset != 0.0 else w).contiguous()
 
     def weight_bytes(self):
         return self.dim * 4

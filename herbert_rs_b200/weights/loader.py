@@ -102,6 +102,8 @@ def fill_model(model, get, rt: Runtime, round_weights_to_bf16: bool = False) -> 
     s = model.spec
     conv = lambda name: convert(get(name), specs[name].role, rt.dtype, rt.device, round_weights_to_bf16)  # noqa: E731
     model.load_embedding(conv(s.embed_name))
+    if s.position_table_name:
+        model.load_position_table(conv(s.position_table_name))
     for i, block in enumerate(model.blocks):
         prefix = model.block_prefix(i)
         model_names = [n for n in specs if n.startswith(prefix)]

@@ -24,7 +24,7 @@ from . import counter_rng
 from .loader import build_model, fill_model
 from .safetensors_io import save_stream
 
-_INIT = {"normal": (0.0, 0.02), "ones_noise": (1.0, 0.1), "wide": (0.0, 1.0)}
+_INIT = {"normal": (0.0, 0.02), "ones_noise": (1.0, 0.1), "zeros_noise": (0.0, 0.1), "wide": (0.0, 1.0)}
 
 
 def random_tensor(name: str, ps, seed: int, device="cpu") -> torch.Tensor:
