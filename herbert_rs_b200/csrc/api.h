@@ -26,24 +26,24 @@ extern "C" {
 
 // attention_decode.cu: decode attention over the paged cache (one query per sequence, keys cut into splits)
 long long hb_attention_decode_scratch_floats(int n_seqs, int nh, int hd, int nsplit);
-int hb_attention_decode_bf16(const void* q, int ldq, void* out, int ldo, const void* kcache, const void*
-    vcache, const int* seq_len, const int* seq_pages, int pages_stride, float* scratch, int n_seqs, int nh,
-    int nkv, int hd, int page_size, int nsplit, float scale, int window, void* stream);
+int hb_attention_decode_bf16(const void* q, int ldq, void* out, int ldo, const void* kcache, const void* vcache,
+    const int* seq_len, const int* seq_pages, int pages_stride, float* scratch, int n_seqs, int nh, int nkv, int hd,
+    int page_size, int nsplit, float scale, int window, float softcap, const float* sink, void* stream);
 int hb_attention_decode_fused_bf16(const void* qkv, int ld, void* out, int ldo, void* kcache, void* vcache,
     const float* qw, const float* kw, float eps, const float* cos_tab, const float* sin_tab, int table_rows,
     int write_cache, const int* seq_len, const int* seq_pages, int pages_stride, float* scratch, int*
     counters, int n_seqs, int nh, int nkv, int page_size, int nsplit, float scale, int window, void* stream);
 
 // attention_prefill.cu: prefill attention, mma.sync flash form, head sizes in steps of 16 up to 256
-int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int ldo, const void* kcache, const void*
-    vcache, const int* seq_start, const int* seq_pos0, const int* seq_pages, int pages_stride, int n_seqs, int
-    max_q_len, int nh, int nkv, int hd, int page_size, float scale, int window, void* stream);
+int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int ldo, const void* kcache, const void* vcache,
+    const int* seq_start, const int* seq_pos0, const int* seq_pages, int pages_stride, int n_seqs, int max_q_len, int
+    nh, int nkv, int hd, int page_size, float scale, int window, float softcap, const float* sink, void* stream);
 
 // attention_prefill_tc.cu: prefill attention on tcgen05 tensor cores, head sizes 64 and 128
 int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens, void* out, int ldo, const void* kcache,
     const void* vcache, int n_pages, const int* seq_start, const int* seq_pos0, const int* seq_pages, int
-    pages_stride, int n_seqs, int max_q_len, int nh, int nkv, int hd, int page_size, float scale, int window,
-    int* error_flag, int* work_counter, void* stream);
+    pages_stride, int n_seqs, int max_q_len, int nh, int nkv, int hd, int page_size, float scale, int window, float
+    softcap, const float* sink, int* error_flag, int* work_counter, void* stream);
 
 // attention_simt.cu: attention of any shape on the CUDA cores (the 32-bit path)
 int hb_attention_simt(int dtype, const void* q, int ldq, void* out, int ldo, const void* kcache, const void*

@@ -41,6 +41,7 @@ struct DecodeArgs {
   float scale;
   int window;
   int stages;
+  float softcap;       // > 0: score <- softcap * tanh(score / softcap) after the scale
 };
 
 // What the fused variant of the keys-as-M kernel needs besides: it takes the raw q/k/v row of each
@@ -198,6 +199,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float v = s[nt][j] * a.scale;
+          if (a.softcap > 0.0f) v = capped_score(v, a.softcap);
           if (edge) {
             const int key = key0 + nt * 8 + 2 * t + (j & 1);
             if (!(key <= p && key >= lo)) v = -INFINITY;
@@ -480,8 +482,10 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
       for (int n = 0; n < NH; ++n) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          float v0 = k0_ok ? s[n][j] * a.scale : -INFINITY;
-          float v1 = k1_ok ? s[n][2 + j] * a.scale : -INFINITY;
+          float v0 = s[n][j] * a.scale, v1 = s[n][2 + j] * a.scale;
+          if (a.softcap > 0.0f) { v0 = capped_score(v0, a.softcap); v1 = capped_score(v1, a.softcap); }
+          v0 = k0_ok ? v0 : -INFINITY;
+          v1 = k1_ok ? v1 : -INFINITY;
           float mx = fmaxf(v0, v1);
           mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
           mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
@@ -635,16 +639,18 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
   }
 }
 
-// out[b][h][:] = sum_s e^{m_s - m} O_s / sum_s e^{m_s - m} l_s
+// out[b][h][:] = sum_s e^{m_s - m} O_s / sum_s e^{m_s - m} l_s.  A sink (a number per head) joins the
+// denominator here, once, whatever the number of splits: m covers it and e^{sink - m} is added.
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                                bf16* __restrict__ out, int ldo, int nh, int hd, int nsplit) {
+                                                bf16* __restrict__ out, int ldo, int nh, int hd, int nsplit,
+                                                const float* __restrict__ sink) {
   pdl_wait();
   pdl_launch();
   const int h = blockIdx.x, b = blockIdx.y;
   const size_t base = ((size_t)b * nh + h) * nsplit;
-  float mm = -INFINITY;
+  float mm = sink ? sink[h] : -INFINITY;
   for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
-  float ll = 0.0f;
+  float ll = sink ? __expf(sink[h] - mm) : 0.0f;
   for (int s = 0; s < nsplit; ++s) {
     const float ms = part_ml[(base + s) * 2];
     if (ms != -INFINITY) ll += __expf(ms - mm) * part_ml[(base + s) * 2 + 1];
@@ -677,8 +683,10 @@ extern "C" long long hb_attention_decode_scratch_floats(int n_seqs, int nh, int 
 extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int ldo, const void* kcache,
                                         const void* vcache, const int* seq_len, const int* seq_pages,
                                         int pages_stride, float* scratch, int n_seqs, int nh, int nkv, int hd,
-                                        int page_size, int nsplit, float scale, int window, void* stream) {
+                                        int page_size, int nsplit, float scale, int window, float softcap,
+                                        const float* sink, void* stream) {
   HB_REQUIRE(n_seqs > 0 && nh > 0 && nkv > 0 && hd > 0, "attention_decode: sizes must be positive");
+  HB_REQUIRE(softcap >= 0.0f, "attention_decode: the cap on the scores must be >= 0 (0: none)");
   HB_REQUIRE(nh % nkv == 0, "attention_decode: %d query heads are not a multiple of %d key/value heads", nh, nkv);
   HB_REQUIRE(nh / nkv <= 16, "attention_decode: at most 16 query heads per key/value head, got %d", nh / nkv);
   HB_REQUIRE(hd % 16 == 0 && hd <= 256, "attention_decode: head size %d must be a multiple of 16, at most 256", hd);
@@ -695,7 +703,7 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
   float* part_o = scratch;
   float* part_ml = scratch + (size_t)n_seqs * nh * nsplit * hd;
   DecodeArgs a{(const bf16*)q, ldq, (const bf16*)kcache, (const bf16*)vcache, seq_len, seq_pages, pages_stride,
-               part_o, part_ml, nh, nkv, hd, page_size, nsplit, scale, window, stages};
+               part_o, part_ml, nh, nkv, hd, page_size, nsplit, scale, window, stages, softcap};
   dim3 grid(nsplit, nkv, n_seqs);
   cudaError_t e;
   if (hd <= 64) {
@@ -723,7 +731,7 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
   }
   HB_CHECK_LAUNCH("attention_decode");
   dim3 cgrid(nh, n_seqs);
-  hb_launch(attention_decode_combine_kernel, dim3(cgrid), dim3(hd >= 128 ? 128 : 64), 0, s, part_o, part_ml, (bf16*)out, ldo, nh, hd, nsplit);
+  hb_launch(attention_decode_combine_kernel, dim3(cgrid), dim3(hd >= 128 ? 128 : 64), 0, s, part_o, part_ml, (bf16*)out, ldo, nh, hd, nsplit, sink);
   HB_CHECK_LAUNCH("attention_decode_combine");
   return 0;
 }

@@ -40,6 +40,8 @@ struct PrefillArgs {
   float scale;
   int window;
   int stages;
+  float softcap;       // > 0: score <- softcap * tanh(score / softcap) after the scale
+  const float* sink;   // [nh] or null: e^{sink} joins the row's sum (m starts at the sink, l at 1)
 };
 
 template <int HDM>
@@ -131,6 +133,10 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillAr
   }
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+  if (a.sink != nullptr) {
+    m[0] = m[1] = a.sink[h];
+    l[0] = l[1] = 1.0f;
+  }
   float o[HDM / 8][4];
 #pragma unroll
   for (int i = 0; i < HDM / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
@@ -176,6 +182,7 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillAr
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float v = s[nt][j] * a.scale;
+          if (a.softcap > 0.0f) v = capped_score(v, a.softcap);
           if (need_mask) {
             const int key = key0 + nt * 8 + 2 * t + (j & 1);
             const bool ok = (j < 2) ? (v0 && key <= p0 && key >= lo0) : (v1 && key <= p1 && key >= lo1);
@@ -250,8 +257,8 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillAr
 extern "C" int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int ldo, const void* kcache,
                                          const void* vcache, const int* seq_start, const int* seq_pos0,
                                          const int* seq_pages, int pages_stride, int n_seqs, int max_q_len,
-                                         int nh, int nkv, int hd, int page_size, float scale, int window,
-                                         void* stream) {
+                                         int nh, int nkv, int hd, int page_size, float scale, int window, float softcap,
+                                         const float* sink, void* stream) {
   HB_REQUIRE(n_seqs > 0 && max_q_len > 0 && nh > 0 && nkv > 0 && hd > 0, "attention_prefill: sizes must be positive");
   HB_REQUIRE(nh % nkv == 0, "attention_prefill: %d query heads are not a multiple of %d key/value heads", nh, nkv);
   HB_REQUIRE(hd % 16 == 0 && hd <= 256, "attention_prefill: head size %d must be a multiple of 16, at most 256", hd);
@@ -260,6 +267,7 @@ extern "C" int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int 
              "attention_prefill: queries and output must be 4-byte aligned");
   HB_REQUIRE(((uintptr_t)kcache & 15) == 0 && ((uintptr_t)vcache & 15) == 0, "attention_prefill: cache must be 16-byte aligned");
   HB_REQUIRE(nh <= 65535 && n_seqs <= 65535, "attention_prefill: grid too large");
+  HB_REQUIRE(softcap >= 0.0f, "attention_prefill: the cap on the scores must be >= 0 (0: none)");
   HB_REQUIRE(window >= 0, "attention_prefill: window must be >= 0");
   HB_REQUIRE((long long)pages_stride * (page_size / AP_TILE) <= AP_PAGE_IDS, "attention_prefill: sequences of more than %d keys are not supported", AP_PAGE_IDS * AP_TILE);
   int stages = 3;
@@ -269,7 +277,7 @@ extern "C" int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int 
     smem = stages * 2 * AP_TILE * (hd * 2 + 16);
   }
   PrefillArgs a{(const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)kcache, (const bf16*)vcache, seq_start, seq_pos0,
-                seq_pages, pages_stride, nh, nkv, hd, page_size, scale, window, stages};
+                seq_pages, pages_stride, nh, nkv, hd, page_size, scale, window, stages, softcap, sink};
   dim3 grid(ceil_div(max_q_len, AP_QTILE), nh, n_seqs);
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t e;

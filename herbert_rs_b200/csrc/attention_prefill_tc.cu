@@ -47,6 +47,9 @@ struct PrefillTcArgs {
   int* error_flag;
   int n_seqs, q_tiles;   // items = q_tiles x n_seqs x nkv x head pairs (some without queries when the sequences differ in length)
   int* work_counter;     // next item; zero when the kernel starts, and left at zero by the CTA that fetches last
+  float scale;           // the scale itself, for the capped form
+  float softcap;         // > 0: score <- softcap * tanh(score * scale / softcap)
+  const float* sink;     // [nh] or null: e^{sink} joins the row's sum (the row starts at m = sink, l = 1)
 };
 
 // One unit of work: 128 consecutive queries of two heads (or one) of one key/value head of one sequence.
@@ -333,6 +336,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
       const int lo_last = (a.window > 0 && p_last - a.window + 1 > 0) ? p_last - a.window + 1 : 0;
       float m = -INFINITY, l = 0.0f;     // m: the maximum the row's P, l and O are scaled to
+      if (a.sink != nullptr) {           // a first "key" without a value: its weight 2^(sink' - m) = 1 is in l already
+        m = a.sink[it.h0 + t] * 1.4426950408889634f;
+        l = 1.0f;
+      }
+      // capped scores are brought to their final form (times log2 e) at once; the plain ones keep the
+      // scale for the fused multiply-add in front of the exponential
+      const float c_log2 = a.softcap > 0.0f ? 1.0f : a.scale_log2;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int ct = c_t + j;
         const int key0 = (tile_lo + j) * PT_KEYS;
@@ -342,6 +352,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int cc = 0; cc < PT_KEYS / 32; ++cc) tc_ld32_issue(tm_s[t] + lane_off + cc * 32, s + cc * 32);
         tc_wait_ld();
+        if (a.softcap > 0.0f) {      // before the mask: the cap would turn -inf into -softcap
+          const float cl = a.softcap * 1.4426950408889634f;
+#pragma unroll
+          for (int i = 0; i < PT_KEYS; ++i) {
+            const float e = fast_exp2(s[i] * (2.0f * a.scale_log2 / a.softcap));      // e^{2 s scale / cap}
+            s[i] = cl - __fdividef(2.0f * cl, 1.0f + e);                               // cap tanh(.) log2 e
+          }
+        }
         const bool need_mask = (key0 + PT_KEYS - 1 > p_first) || (key0 < lo_last);
         if (need_mask) {
 #pragma unroll
@@ -356,7 +374,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
           for (int q = 0; q < 4; ++q) mxs[q] = max3(mxs[q], s[i + 2 * q], s[i + 2 * q + 1]);
         float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
-        mx *= a.scale_log2;         // the scale is positive: the maximum of the raw scores is the maximum
+        mx *= c_log2;               // the scale is positive: the maximum of the raw scores is the maximum
         const bool raise = mx > m + PT_RAISE || (m == -INFINITY && mx > -INFINITY);
         if (j > 0 && __any_sync(0xffffffffu, raise)) {
           // rescale O to the new maximum (rows that keep theirs: factor 1); the product of the tile before must be complete
@@ -379,7 +397,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const float m_use = (m == -INFINITY) ? 0.0f : m;
         // P = 2^(s*c - m) as bfloat16 pairs; masked scores are -inf and give 0
         unsigned pk[PT_KEYS / 2];
-        const unsigned long long c2 = pack2(a.scale_log2, a.scale_log2), m2 = pack2(-m_use, -m_use);
+        const unsigned long long c2 = pack2(c_log2, c_log2), m2 = pack2(-m_use, -m_use);
         unsigned long long sum2 = pack2(0.0f, 0.0f);
 #pragma unroll
         for (int i = 0; i < PT_KEYS; i += 2) {
@@ -450,8 +468,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens, void* out, int ldo, const void* kcache,
                                             const void* vcache, int n_pages, const int* seq_start, const int* seq_pos0,
                                             const int* seq_pages, int pages_stride, int n_seqs, int max_q_len, int nh,
-                                            int nkv, int hd, int page_size, float scale, int window, int* error_flag,
-                                            int* work_counter, void* stream) {
+                                            int nkv, int hd, int page_size, float scale, int window, float softcap,
+                                            const float* sink, int* error_flag, int* work_counter, void* stream) {
   HB_REQUIRE(n_seqs > 0 && max_q_len > 0 && nh > 0 && nkv > 0 && n_tokens > 0 && n_pages > 0, "attention_prefill_tc: sizes must be positive");
   HB_REQUIRE(hd == 64 || hd == 128, "attention_prefill_tc: head size %d is not 64 or 128", hd);
   HB_REQUIRE(nh % nkv == 0, "attention_prefill_tc: %d query heads are not a multiple of %d key/value heads", nh, nkv);
@@ -462,6 +480,7 @@ extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens
   HB_REQUIRE(nh <= 65535 && n_seqs <= 65535 && window >= 0 && error_flag != nullptr && work_counter != nullptr,
              "attention_prefill_tc: bad arguments (an error flag and a work counter, one int each, are required)");
   HB_REQUIRE(scale > 0.0f, "attention_prefill_tc: the score scale must be positive");
+  HB_REQUIRE(softcap >= 0.0f, "attention_prefill_tc: the cap on the scores must be >= 0 (0: none)");
   CUtensorMap mq, mk, mv;
   int rc = make_map_cols(&mq, q, n_tokens, nh * hd, ldq, PT_Q);
   if (rc) return rc;
@@ -472,7 +491,7 @@ extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens
   if (rc) return rc;
   const int q_tiles = ceil_div(max_q_len, PT_Q);
   PrefillTcArgs a{(bf16*)out, ldo, seq_start, seq_pos0, seq_pages, pages_stride, nh, nkv, page_size,
-                  scale * 1.4426950408889634f, window, error_flag, n_seqs, q_tiles, work_counter};
+                  scale * 1.4426950408889634f, window, error_flag, n_seqs, q_tiles, work_counter, scale, softcap, sink};
   cudaStream_t s = (cudaStream_t)stream;
   const int pairs = (nh / nkv + 1) / 2;
   const long long items = (long long)q_tiles * n_seqs * nkv * pairs;

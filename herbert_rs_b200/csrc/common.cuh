@@ -79,6 +79,15 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
 
+// ---- a cap on attention scores ---------------------------------------------------------------
+// cap * tanh(s / cap) with tanh(x) = 1 - 2 / (1 + e^{2x}): one exponential and one division of the
+// fast kind, absolute error about 1e-7 * cap (e^{2x} = inf gives 1, 0 gives -1).  The 32-bit path
+// uses tanhf instead.
+__device__ __forceinline__ float capped_score(float s, float cap) {
+  const float e = __expf(2.0f * __fdividef(s, cap));
+  return cap * (1.0f - __fdividef(2.0f, 1.0f + e));
+}
+
 // ---- reductions -----------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

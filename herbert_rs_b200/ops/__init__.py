@@ -56,15 +56,15 @@ _SIGS = {
     "hb_attention_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p],
     "hb_attention_decode_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p],
     "hb_attention_decode_fused_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                                        c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_prefill_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p],
     "hb_attention_prefill_tc_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
-                                     c_void_p],
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p,
+                                     c_void_p, c_void_p, c_void_p],
     "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p],
     "hb_gemm_skinny_norm_parts": [c_int, c_int],
     "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -912,15 +912,19 @@ def decode_splits(n_seqs: int, num_kv_heads: int, max_tiles: int, device=None) -
 
 
 def attention_decode(q, ldq, out, k_cache, v_cache, seq_len, seq_pages, scratch, num_heads, num_kv_heads,
-                     head_dim, page_size, nsplit, scale, window) -> None:
-    """One query per sequence (row b of q) over the cache; scratch holds the splits' partial results."""
+                     head_dim, page_size, nsplit, scale, window, softcap=None, sink=None) -> None:
+    """One query per sequence (row b of q) over the cache; scratch holds the splits' partial results.
+    softcap and sink as in `attention`; the sink joins the denominator where the splits are combined."""
+    if sink is not None:
+        _check(sink, torch.float32, "sink")
     _check(out, torch.bfloat16, "out"); _check(scratch, torch.float32, "scratch")
     n = out.shape[0]
     if scratch.numel() < attention_decode_scratch_floats(n, num_heads, head_dim, nsplit):
         raise BackendError("attention_decode: scratch is too small")
     _run("hb_attention_decode_bf16", q.data_ptr(), int(ldq), out.data_ptr(), out.stride(0), k_cache.data_ptr(),
          v_cache.data_ptr(), seq_len.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0), scratch.data_ptr(),
-         n, num_heads, num_kv_heads, head_dim, page_size, int(nsplit), float(scale), int(window or 0), _stream())
+         n, num_heads, num_kv_heads, head_dim, page_size, int(nsplit), float(scale), int(window or 0),
+         float(softcap or 0.0), _ptr(sink), _stream())
 
 
 _DECODE_COUNTERS = 65536
@@ -953,23 +957,27 @@ def attention_decode_fused(qkv, out, k_cache, v_cache, q_weight, k_weight, eps, 
 
 
 def attention_prefill(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq_pages, n_seqs, max_q_len,
-                      num_heads, num_kv_heads, head_dim, page_size, scale, window) -> None:
+                      num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap=None, sink=None) -> None:
     """Causal attention of packed query rows (seq_start marks the sequences) over the cache."""
     _check(out, torch.bfloat16, "out")
+    if sink is not None:
+        _check(sink, torch.float32, "sink")
     _run("hb_attention_prefill_bf16", q.data_ptr(), int(ldq), out.data_ptr(), out.stride(0), k_cache.data_ptr(),
          v_cache.data_ptr(), seq_start.data_ptr(), seq_pos0.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0),
          int(n_seqs), int(max_q_len), num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
-         _stream())
+         float(softcap or 0.0), _ptr(sink), _stream())
 
 
 def attention_prefill_tc(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq_pages, n_seqs, max_q_len,
-                         num_heads, num_kv_heads, head_dim, page_size, scale, window) -> None:
+                         num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap=None, sink=None) -> None:
     """The same on tcgen05 tensor cores (head sizes 64 and 128): S and O in tensor memory."""
     _check(out, torch.bfloat16, "out")
+    if sink is not None:
+        _check(sink, torch.float32, "sink")
     _run("hb_attention_prefill_tc_bf16", q.data_ptr(), int(ldq), q.shape[0], out.data_ptr(), out.stride(0),
          k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[0], seq_start.data_ptr(), seq_pos0.data_ptr(),
          seq_pages.data_ptr(), seq_pages.stride(0), int(n_seqs), int(max_q_len), num_heads, num_kv_heads, head_dim,
-         page_size, float(scale), int(window or 0), _error_flag(out.device).data_ptr(),
+         page_size, float(scale), int(window or 0), float(softcap or 0.0), _ptr(sink), _error_flag(out.device).data_ptr(),
          _work_counter(out.device).data_ptr(), _stream())
 
 
@@ -1005,8 +1013,9 @@ def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, hea
 
     bfloat16 steps of one token per sequence take the split-key tensor-core kernel, other bfloat16
     steps the flash kernel; head sizes or pages those cannot serve, and the float32 path, take
-    the any-shape kernel."""
-    if softcap or sink is not None:
+    the any-shape kernel.  Every kernel takes a cap on the scores (softcap c: s <- c * tanh(s / c)) and a sink
+    (a float per query head whose exponential joins the softmax's denominator); v_cache may be k_cache."""
+    if options.attention == "simt":
         attention_simt(q, ldq, out, k_cache, v_cache, batch.tok_seq, batch.tok_pos, seq_pages, num_heads,
                        num_kv_heads, head_dim, page_size, scale, window, softcap, sink)
         return
@@ -1015,15 +1024,15 @@ def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, hea
         nsplit = decode_splits(batch.n_seqs, num_kv_heads, tiles)
         buf = scratch((attention_decode_scratch_floats(batch.n_seqs, num_heads, head_dim, nsplit),), torch.float32)
         attention_decode(q, ldq, out, k_cache, v_cache, batch.seq_len, seq_pages, buf, num_heads, num_kv_heads,
-                         head_dim, page_size, nsplit, scale, window)
+                         head_dim, page_size, nsplit, scale, window, softcap, sink)
         return
     if _prefill_tc_ok(q, ldq, out, head_dim, page_size):
         attention_prefill_tc(q, ldq, out, k_cache, v_cache, batch.seq_start, batch.seq_pos0, seq_pages, batch.n_seqs,
-                             batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window)
+                             batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap, sink)
         return
     if _prefill_kernel_ok(out, head_dim, page_size):
         attention_prefill(q, ldq, out, k_cache, v_cache, batch.seq_start, batch.seq_pos0, seq_pages, batch.n_seqs,
-                          batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window)
+                          batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window, softcap, sink)
         return
     attention_simt(q, ldq, out, k_cache, v_cache, batch.tok_seq, batch.tok_pos, seq_pages, num_heads,
                    num_kv_heads, head_dim, page_size, scale, window, softcap, sink)

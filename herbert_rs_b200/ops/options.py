@@ -22,6 +22,9 @@ class KernelOptions:
     prefill_split_tiles: bool = True
     # Head size 128, decode: norm, rotation, cache write, attention and combine in one launch.
     decode_fused: bool = True
+    # Attention over cached keys and values: "auto" (the tensor-core kernels where dtype and sizes allow), or
+    # "simt" (the any-shape kernel on the CUDA cores for every step).
+    attention: str = "auto"
     # Prefill attention for head sizes 64 and 128: "tcgen05", or "mma" (the mma.sync kernel for every size).
     prefill_attention: str = "tcgen05"
     # Decode attention cuts the keys so that this many CTAs stand on every SM.

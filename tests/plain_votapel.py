@@ -120,8 +120,9 @@ def route(scores, groups, keep, top):
     return sorted(allowed, key=lambda e: (-float(scores[e]), e))[:top]
 
 
-def routed_ff(h, w, f, dtype, store=_keep):
-    """The mixture on normed input h [T, D]; w: the feed-forward's tensors by local name."""
+def routed_ff(h, w, f, dtype, store=_keep, log=None):
+    """The mixture on normed input h [T, D]; w: the feed-forward's tensors by local name.  `log`, a list,
+    receives (router logits [E], chosen experts) per token."""
     r = f["router"]
     E, top = r["experts"], r["top"]
     gr = r.get("groups") or {"count": 1, "keep": 1}
@@ -129,7 +130,10 @@ def routed_ff(h, w, f, dtype, store=_keep):
     s = torch.sigmoid(z)
     out = torch.zeros(h.shape[0], w["e0.down"].shape[0], dtype=dtype)
     for t in range(h.shape[0]):
-        for e in route(s[t], gr["count"], gr["keep"], top):
+        chosen = route(s[t], gr["count"], gr["keep"], top)
+        if log is not None:
+            log.append((z[t].clone(), chosen))
+        for e in chosen:
             y = gated_expert(h[t:t + 1], w[f"e{e}.gate"].to(dtype), w[f"e{e}.up"].to(dtype), w[f"e{e}.down"].to(dtype), store)
             out[t] += (s[t, e] * r.get("scale", 1.0)).to(dtype) * y[0]
     if f.get("shared"):
@@ -139,18 +143,20 @@ def routed_ff(h, w, f, dtype, store=_keep):
 
 # ---- the model ----------------------------------------------------------------------------------
 class PlainVotapel:
-    def __init__(self, folder: str):
-        with open(os.path.join(folder, "config.json")) as f:
-            self.cfg = json.load(f)
-        self.w = read_safetensors(os.path.join(folder, "model.safetensors"))
+    def __init__(self, folder: str = None, config: dict = None, tensors: dict = None):
+        if folder is not None:
+            with open(os.path.join(folder, "config.json")) as f:
+                config = json.load(f)
+            tensors = read_safetensors(os.path.join(folder, "model.safetensors"))
+        self.cfg, self.w = config, tensors
         self.vocab = self.cfg["vocab"]
 
     def _sub(self, prefix):
         return {k[len(prefix):]: v for k, v in self.w.items() if k.startswith(prefix)}
 
-    def hidden(self, ids: Sequence[int], dtype=torch.float64, store=_keep, layers_out=None):
+    def hidden(self, ids: Sequence[int], dtype=torch.float64, store=_keep, layers_out=None, routes_out=None):
         """The residual stream after the last layer, [T, D]; `layers_out`, a list, receives it after
-        every layer."""
+        every layer, `routes_out` every token's router logits and choice, layer by layer."""
         c = self.cfg
         T = len(ids)
         pos = list(range(T))
@@ -160,7 +166,7 @@ class PlainVotapel:
             h = store(offset_rms_norm(x, self.w[f"l{i}.norm1"].to(dtype), eps))
             y = attention_mixer(h, self._sub(f"l{i}.mix."), layer["mixer"], pos, dtype, store)
             if layer.get("mlp"):
-                y = y + routed_ff(h, self._sub(f"l{i}.mlp."), layer["mlp"], dtype, store)
+                y = y + routed_ff(h, self._sub(f"l{i}.mlp."), layer["mlp"], dtype, store, routes_out)
             x = x + mult * y
             if layers_out is not None:
                 layers_out.append(x.clone())
