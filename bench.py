@@ -206,6 +206,29 @@ def _kebisun_config(width, heads, dim, rot, vdim, kv_rank, q_rank, window, gla_h
             "layers": layers}
 
 
+def _votapel_config(width, heads, kv_heads, dim, experts, top, groups, keep, expert_ff, shared_ff, vocab, layers=4,
+                    max_positions=8192):
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+             "q_temp": {"coef": 0.1, "every": 1024}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff},
+           "router": {"experts": experts, "top": top, "scale": 1.0, "groups": {"count": groups, "keep": keep}}}
+    return {"architecture": "Votapel", "vocab": vocab, "width": width, "max_positions": max_positions, "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "layers": [{"type": "attention", "mixer": mixer, "mlp": moe} for _ in range(layers)]}
+
+
+VOTAPEL_SIZES = {
+    # Votapel layer sizes, and the dense decoder of the same width, depth, heads and head size beside them; a token's
+    # experts and the shared one together are as wide as the dense feed-forward
+    "1k": (dict(width=1024, heads=16, kv_heads=8, dim=64, experts=16, top=2, groups=4, keep=2, expert_ff=768, shared_ff=1536,
+                vocab=32000),
+           dict(hidden_size=1024, num_hidden_layers=4, num_attention_heads=16, num_key_value_heads=8, head_dim=64,
+                intermediate_size=3072, vocab_size=32000, eos_token_id=31999)),
+    "2k": (dict(width=2048, heads=16, kv_heads=8, dim=128, experts=32, top=4, groups=8, keep=4, expert_ff=1408, shared_ff=2560,
+                vocab=32000),
+           dict(hidden_size=2048, num_hidden_layers=4, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+                intermediate_size=8192, vocab_size=32000, eos_token_id=31999)),
+}
+
 DESIGN_SIZES = {
     # Kebisun layer sizes, and the dense decoder of the same width, depth and feed-forward width beside them
     "1k": (dict(width=1024, heads=8, dim=64, rot=32, vdim=64, kv_rank=256, q_rank=384, window=4096, gla_heads=4, gla_dk=128,
@@ -240,6 +263,19 @@ def _launcher_work(name, n, ctx):
         if name in ("hb_moe_experts", "hb_moe_experts_grouped_bf16"):
             E, top, F = ctx["experts"], ctx["top"], ctx["expert_ff"]
             return n * 4.0 * T * top * F * D, n * (min(E, T * top) * 2 * F * D * es + T * D * (es + 4))
+    elif ctx["kind"] == "votapel":
+        H, KV, hd, D = ctx["heads"], ctx["kv_heads"], ctx["dim"], ctx["width"]
+        if name in ("hb_attention_prefill_tc_bf16", "hb_attention_prefill_bf16", "hb_attention_decode_bf16", "hb_attention_simt"):
+            return n * 4.0 * pairs * H * hd, n * (B * L * KV * hd * es + 2 * T * H * hd * es)      # one plane: the values are the keys
+        if name == "hb_scaled_residual_norm":
+            return n * 6.0 * T * D, n * T * D * (4 + 4 + 4 + es)
+        if name == "hb_qk_prepare_cache":
+            return n * 2.0 * T * (H + KV) * hd, n * T * (H + KV) * hd * (4 + es)
+        if name in ("hb_moe_experts", "hb_moe_experts_grouped_bf16"):
+            E, top, F = ctx["experts"], ctx["top"], ctx["expert_ff"]
+            return n * 6.0 * T * top * F * D, n * (min(E, T * top) * 3 * F * D * es + T * D * (es + 4))
+        if name == "hb_moe_route":
+            return n * 2.0 * T * ctx["experts"] * D, n * (T * D * es + ctx["experts"] * D * es)
     else:
         H, KV, hd, D = ctx["heads"], ctx["kv_heads"], ctx["head_dim"], ctx["width"]
         if name in ("hb_attention_prefill_tc_bf16", "hb_attention_prefill_bf16", "hb_attention_decode_bf16",
@@ -317,7 +353,7 @@ def _design_point(hb, ops, torch, np, cfg, ctx, pk, prompt_len, batch, steps, wa
 
 
 def run_design(args) -> int:
-    """`--design kebisun`: prefill and decode of the Kebisun design at layer sizes that resemble a real
+    """`--design kebisun|votapel`: prefill and decode of that design at layer sizes that resemble a real
     model's, beside the dense decoder of equal width, depth and feed-forward width (random weights,
     bfloat16, four layers each)."""
     import numpy as np
@@ -330,20 +366,21 @@ def run_design(args) -> int:
     sampler, windows = ClockSampler(), []
     sampler.start()
     result = {}
-    for size in (sorted(DESIGN_SIZES) if args.design_size == "all" else [args.design_size]):
-        kb, dense = DESIGN_SIZES[size]
-        kcfg = _kebisun_config(**kb)
+    table, make = (DESIGN_SIZES, _kebisun_config) if args.design == "kebisun" else (VOTAPEL_SIZES, _votapel_config)
+    for size in (sorted(table) if args.design_size == "all" else [args.design_size]):
+        kb, dense = table[size]
+        kcfg = make(**kb)
         qcfg = dict(QWEN3_8B)
         qcfg.update(dense)
-        kctx = dict(kb, kind="kebisun")
+        kctx = dict(kb, kind=args.design)
         qctx = dict(kind="dense", heads=dense["num_attention_heads"], kv_heads=dense["num_key_value_heads"],
                     head_dim=dense["head_dim"], width=dense["hidden_size"])
         result[size] = {
-            "kebisun": _design_point(hb, ops, torch, np, kcfg, kctx, pk, args.prompt_len, args.batch, args.steps, args.warmup, windows),
+            args.design: _design_point(hb, ops, torch, np, kcfg, kctx, pk, args.prompt_len, args.batch, args.steps, args.warmup, windows),
             "dense": _design_point(hb, ops, torch, np, qcfg, qctx, pk, args.prompt_len, args.batch, args.steps, args.warmup, windows),
         }
     sampler.stop()
-    print(json.dumps({"metric": "Kebisun and the dense decoder at equal sizes: prefill and decode tokens/s", "unit": "tokens/s",
+    print(json.dumps({"metric": f"{args.design.capitalize()} and the dense decoder at equal sizes: prefill and decode tokens/s", "unit": "tokens/s",
                       "n_gpus": 1, "impl": "ours", "dtype": "bf16", "data": "synthetic", "steps": args.steps, "warmup": args.warmup,
                       "config": {"prompt_len": args.prompt_len, "batch": args.batch, "layers": 4,
                                  "timing": "CUDA events; every decode step reads all weights, a prompt step reads activations larger than L2 at the 2k size"},
@@ -371,7 +408,7 @@ def main() -> int:
     ap.add_argument("--pdl-graph", type=int, default=None, help="programmatic dependent launch inside recorded decode steps (0, 1, 2)")
     ap.add_argument("--workload", default=None, choices=["0.6b", "32b"],
                     help="run only this workload of the baseline and print its line")
-    ap.add_argument("--design", default=None, choices=["kebisun"],
+    ap.add_argument("--design", default=None, choices=["kebisun", "votapel"],
                     help="measure this design beside the dense decoder at equal sizes instead of the headline workload")
     ap.add_argument("--design-size", default="all", choices=["all"] + sorted(DESIGN_SIZES))
     args = ap.parse_args()

@@ -49,7 +49,8 @@ class RoutedFeedForward(FeedForward):
 
     def param_specs(self):
         s = self.spec
-        p = {s.router_name: ParamSpec((s.num_experts, s.hidden_size), init="wide")}
+        # random sigmoid routers stay small: wide logits would all score exactly 1 and tie
+        p = {s.router_name: ParamSpec((s.num_experts, s.hidden_size), init="wide" if s.score == "softmax" else "normal")}
         for e in range(s.num_experts):
             names = self._names(e)
             for n in names[:-1]:
