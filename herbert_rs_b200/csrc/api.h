@@ -103,6 +103,8 @@ long long hb_gemm_tcgen05_workspace_floats(int ctas);
 int hb_gemm_tcgen05_set_workspace(float* floats, int* counters, int ctas);
 int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int
     K, int epi, int* error_flag, void* stream);
+int hb_gemm_tcgen05_grouped_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M_max, int
+    N, int K, int E, int epi, const int* rows_used, const int* tile_expert, int* error_flag, void* stream);
 int hb_gemm_tcgen05_qkv_ok(int M, int N);
 int hb_gemm_tcgen05_qkv_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N,
     int K, const float* in_sumsq, int in_parts, int in_stride, float in_eps, const float* qw, const float* kw,
@@ -156,6 +158,10 @@ int hb_moe_experts(int dtype, const void* h, int ld, const void* up, const void*
     float* weights, void* mid, float* y, int ldy, int n_tokens, int D, int F, int top, int act, int gated, int
     accumulate, void* stream);
 long long hb_moe_grouped_scratch_ints(int n_tokens, int E, int top);
+int hb_moe_experts_tc_rows(int n_tokens, int E, int top);
+int hb_moe_experts_tc_bf16(const void* h, int ld, const void* up, const void* down, const int* ids, const float*
+    weights, int* ints, void* sorted, void* mid, float* part, float* y, int ldy, int n_tokens, int D, int E, int F,
+    int top, int accumulate, int* error_flag, void* stream);
 int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up, const void* down, const int* ids, const
     float* weights, int* scratch, void* mid, float* part, float* y, int ldy, int n_tokens, int D, int E, int F, int
     top, int act, int gated, int accumulate, void* stream);

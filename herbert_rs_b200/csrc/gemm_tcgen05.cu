@@ -61,6 +61,13 @@ struct TgSched {
   int per;           // k blocks per CTA in that part (< k blocks of a tile: a CTA touches at most two tiles)
   float* ws;         // [G][2] pieces of 128 x BN floats, each stored as [BN / 4][128][4]
   int* counters;     // [sk_tiles], zero between launches
+  // A product grouped by expert (null / 0 otherwise): the rows of A are sorted by expert, each expert's run padded
+  // to whole tiles of 128 rows; tile i of A belongs to expert tile_expert[i], whose weights are rows
+  // tile_expert[i] * expert_rows + (0..N) of W; *rows_used (written on the device by the kernel that sorted the
+  // rows) says how many rows of A are in use.  No tile is shared between CTAs then (sk_tiles = 0).
+  const int* rows_used;
+  const int* tile_expert;
+  int expert_rows;
 };
 
 struct TgSegments {
@@ -115,8 +122,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   auto acc_empty = [&](int b) { return bars + (2 * STAGES + 2 + b) * 8; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (M + TG_BM - 1) / TG_BM, tiles_n = (N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
+  int tiles_m = (M + TG_BM - 1) / TG_BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + TG_BK - 1) / TG_BK;
 
   if (threadIdx.x == 0) {
@@ -140,6 +148,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   pdl_wait();
   pdl_launch();
   const unsigned tmem_base = *tmem_slot;
+  if (sc.rows_used != nullptr) {      // grouped by expert: every thread reads the same count, so all roles walk the same tiles
+    int used = *sc.rows_used;
+    used = used < 0 ? 0 : (used > M ? M : used);
+    M = used;
+    tiles_m = (used + TG_BM - 1) / TG_BM;
+    num_tiles = tiles_m * tiles_n;
+  }
 
   // Tiles in the order m fastest: CTAs that run side by side share the same slab of W in L2.
   if (warp == 0) {
@@ -149,7 +164,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       TgSegments segs(sc, num_tiles, num_kb);
       int tile, kb0, kb1;
       while (ok && segs.next(tile, kb0, kb1)) {
-        const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
+        const int m0 = (tile % tiles_m) * TG_BM;
+        int n0 = (tile / tiles_m) * BN;
+        if (sc.tile_expert != nullptr) n0 += sc.tile_expert[tile % tiles_m] * sc.expert_rows;      // this expert's rows of W
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(empty_bar(s), ((it / STAGES) - 1) & 1)) {
@@ -647,9 +664,16 @@ static int tg_dispatch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* 
   HB_FAIL(2, "gemm_tcgen05: unknown epilogue %d", epi);
 }
 
+// The facts of a product grouped by expert (see TgSched); all null / 0 for a plain product.
+struct TgGrouped {
+  const int* rows_used = nullptr;
+  const int* tile_expert = nullptr;
+  int expert_rows = 0;
+};
+
 template <int BN, int EPI, bool NORM>
 static int tg_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int M, int N, int K, int* err,
-                     cudaStream_t s, const TgNorm& nm) {
+                     cudaStream_t s, const TgNorm& nm, const TgGrouped& grp = TgGrouped{}) {
   const int smem = TgSmem<BN>::kBytes;
   static bool configured = false;
   if (!configured) {
@@ -666,14 +690,14 @@ static int tg_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int 
   const int tiles = ceil_div(M, TG_BM) * ceil_div(N, BN);
   const int num_kb = ceil_div(K, TG_BK);
   int G = tiles < sms ? tiles : sms;
-  TgSched sc{ceil_div(tiles, G), 0, 0, 1, nullptr, nullptr};
+  TgSched sc{ceil_div(tiles, G), 0, 0, 1, nullptr, nullptr, grp.rows_used, grp.tile_expert, grp.expert_rows};
   // Leftover tiles are cut into equal runs of k blocks when that pays: a workspace is there, the
   // leftover would leave at least half of the GPU idle, and a run is at least a few k blocks.
   // (Measured at the 8B sizes: with 48 leftover tiles the down projection takes 62 instead of 88 us;
   // with 108 or 128 leftover tiles the products with K = 4096..12288 get slower, because CTAs that
   // start at different k no longer share the weight slabs in L2 in lockstep.)
   const int rem = tiles % sms;
-  if (tg_splits_tiles(tiles, num_kb, sms)) {
+  if (grp.tile_expert == nullptr && tg_splits_tiles(tiles, num_kb, sms)) {
     G = sms;
     sc.full_rounds = tiles / sms;
     sc.sk_tiles = rem;
@@ -762,6 +786,43 @@ extern "C" int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int l
   if (const int went = tg_try_ksplit(false, A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, none)) return went > 0 ? 0 : -went;
   return BN == 256 ? tg_dispatch<256, false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none)
                    : tg_dispatch<128, false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none);
+}
+
+// A product grouped by expert: A [M_max, K] holds rows sorted by expert, each expert's run padded to whole tiles of
+// 128 rows; W [E * N, K] stacks the experts' matrices; tile i of A (128 rows) is multiplied by the matrix of expert
+// tile_expert[i]; only the first *rows_used rows are computed (both written on the device before this launch).
+// C [M_max, N] (EPI_STORE, EPI_STORE_F32) or [M_max, N / 2] (EPI_SWIGLU).  Rows of padding are computed and mean nothing.
+extern "C" int hb_gemm_tcgen05_grouped_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M_max,
+                                            int N, int K, int E, int epi, const int* rows_used, const int* tile_expert,
+                                            int* error_flag, void* stream) {
+  HB_REQUIRE(M_max > 0 && N > 0 && K > 0 && E > 0, "gemm_tcgen05_grouped: sizes must be positive");
+  HB_REQUIRE(M_max % TG_BM == 0, "gemm_tcgen05_grouped: %d rows are not whole tiles of %d", M_max, TG_BM);
+  HB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05_grouped: K (%d) and the leading dimensions (%d, %d) must be multiples of 8", K, lda, ldw);
+  HB_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tcgen05_grouped: operands must be 16-byte aligned");
+  HB_REQUIRE(epi == HB_EPI_STORE || epi == HB_EPI_STORE_F32 || (epi == HB_EPI_SWIGLU && N % 16 == 0),
+             "gemm_tcgen05_grouped: epilogue %d with N=%d is not served", epi, N);
+  HB_REQUIRE(rows_used != nullptr && tile_expert != nullptr && error_flag != nullptr, "gemm_tcgen05_grouped: needs the row count, the tiles' experts and an error flag");
+  HB_REQUIRE((long long)E * N < 2147483647LL, "gemm_tcgen05_grouped: too many weight rows");
+  CUtensorMap ma, mw;
+  const int BN = N <= 128 ? 128 : 256;
+  int rc = make_map(&ma, A, M_max, K, lda, TG_BM);
+  if (rc) return rc;
+  rc = make_map(&mw, W, E * N, K, ldw, BN);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  const TgNorm none{};
+  TgGrouped grp;
+  grp.rows_used = rows_used;
+  grp.tile_expert = tile_expert;
+  grp.expert_rows = N;
+  if (BN == 256) {
+    if (epi == HB_EPI_SWIGLU) return tg_launch<256, HB_EPI_SWIGLU, false>(ma, mw, C, ldc, M_max, N, K, error_flag, s, none, grp);
+    if (epi == HB_EPI_STORE) return tg_launch<256, HB_EPI_STORE, false>(ma, mw, C, ldc, M_max, N, K, error_flag, s, none, grp);
+    return tg_launch<256, HB_EPI_STORE_F32, false>(ma, mw, C, ldc, M_max, N, K, error_flag, s, none, grp);
+  }
+  if (epi == HB_EPI_SWIGLU) return tg_launch<128, HB_EPI_SWIGLU, false>(ma, mw, C, ldc, M_max, N, K, error_flag, s, none, grp);
+  if (epi == HB_EPI_STORE) return tg_launch<128, HB_EPI_STORE, false>(ma, mw, C, ldc, M_max, N, K, error_flag, s, none, grp);
+  return tg_launch<128, HB_EPI_STORE_F32, false>(ma, mw, C, ldc, M_max, N, K, error_flag, s, none, grp);
 }
 
 // The q/k/v product of an attention layer with heads of 128 and full rotation, for steps of 512 rows

@@ -7,8 +7,10 @@
 // of neighbours, a group's score being the sum of its `group_top` largest s, with only the experts of
 // the `keep` best groups open to the choice (ties between groups, as between experts, go to the
 // lower index); a factor on every weight.  Option of the experts: a gated form
-// Down_e (act(Gate_e h) * (Up_e h)), with the rows of Gate_e and Up_e stored in turn (row 2f: gate f,
-// row 2f + 1: up f) so that one thread of a tile holds both halves of a channel.
+// Down_e (act(Gate_e h) * (Up_e h)) whose first matrix has 2F rows per expert: `gated` 2: the rows of
+// Gate_e and Up_e in turn in groups of 8 (8 gate rows, the 8 up rows of the same channels, ...: the layout
+// of the dense gated feed-forward, so that a thread of a tensor-core tile holds both halves of a
+// channel); `gated` 1: all gate rows, then all up rows (any F; the few-token kernel only).
 //
 // Three launches, all reading the choice from device memory (nothing of it is known to the host, so
 // a recorded step can be replayed): the router with softmax and choice; the chosen experts' first
@@ -162,7 +164,7 @@ __device__ __forceinline__ float moe_act(float z, int act) {
   return z / (1.0f + expf(-z));
 }
 
-// mid[(t*top + r), f] = act(Up_e[f, :] . h[t, :]),  e = ids[t, r]; gated: act(row 2f . h) * (row 2f + 1 . h) of
+// mid[(t*top + r), f] = act(Up_e[f, :] . h[t, :]),  e = ids[t, r]; gated: act(gate row f . h) * (up row f . h) of
 // the expert's 2F rows.  One warp per output.
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
@@ -176,8 +178,9 @@ moe_up_kernel(const T* __restrict__ h, int ld, const T* __restrict__ up, const i
   const int e = ids[u];
   const T* hr = h + (size_t)(u / top) * ld;
   if (gated) {
-    const T* w = up + ((size_t)e * 2 * F + 2 * f) * D;
-    const float g = warp_dot(hr, w, D, lane), v = warp_dot(hr, w + D, D, lane);
+    const int grow = gated == 2 ? (f >> 3) * 16 + (f & 7) : f, urow = gated == 2 ? grow + 8 : F + f;
+    const T* w = up + (size_t)e * 2 * F * D;
+    const float g = warp_dot(hr, w + (size_t)grow * D, D, lane), v = warp_dot(hr, w + (size_t)urow * D, D, lane);
     if (lane == 0) mid[(size_t)u * F + f] = from_f32<T>(moe_act(g, act) * v);
     return;
   }
@@ -280,7 +283,8 @@ moe_group_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restric
 
 // C[pair, n] = sum_k A[row(pair), k] * W[e][n][k] for the pairs of tile blockIdx.x of its expert.
 // UP: row(pair) = pair / top of h, C = act(.) as bfloat16 into mid[pair]; else row(pair) = pair of mid, C float into part[pair].
-// UP and gated: W has 2F rows per expert, gate and up in turn, and C[pair, n / 2] = act(even column) * (odd column).
+// UP and gated: W has 2F rows per expert, gate and up in turn in groups of 8, and a thread's columns of fragment nt (even: gate)
+// and nt + 1 (up) are the two halves of its channels.
 template <bool UP>
 __global__ void __launch_bounds__(MG_THREADS)
 moe_grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, void* __restrict__ C, int ldc,
@@ -378,12 +382,14 @@ moe_grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restr
       if (pair < 0) continue;
       if (UP && gated) {
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-          const int n = n0 + wn + nt * 8 + 2 * t;      // even: the gate's column; N is even, so n + 1 < N too
-          if (n >= N) continue;
-          ((bf16*)C)[(size_t)pair * ldc + (n >> 1)] =
-              __float2bfloat16_rn(moe_act(acc[m][nt][half * 2], act) * acc[m][nt][half * 2 + 1]);
-        }
+        for (int nt = 0; nt < 8; nt += 2)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int n = n0 + wn + nt * 8 + 2 * t + c;      // a gate column; its up column is n + 8 (N is a multiple of 16)
+            if (n >= N) continue;
+            ((bf16*)C)[(size_t)pair * ldc + ((n0 + wn + nt * 8) >> 1) + 2 * t + c] =
+                __float2bfloat16_rn(moe_act(acc[m][nt][half * 2 + c], act) * acc[m][nt + 1][half * 2 + c]);
+          }
         continue;
       }
 #pragma unroll
@@ -399,14 +405,18 @@ moe_grouped_gemm_kernel(const bf16* __restrict__ A, int lda, const bf16* __restr
     }
 }
 
+// slot: where each pair's row lies in `part` (null: at the pair's own index)
 __global__ void moe_combine_kernel(const float* __restrict__ part, const float* __restrict__ wts, float* __restrict__ y, int ldy,
-                                   int D, int top, int accumulate) {
+                                   int D, int top, int accumulate, const int* __restrict__ slot) {
   pdl_wait();
   pdl_launch();
   const int t = blockIdx.y, d = blockIdx.x * blockDim.x + threadIdx.x;
   if (d >= D) return;
   float acc = 0.0f;
-  for (int r = 0; r < top; ++r) acc = fmaf(wts[(size_t)t * top + r], part[((size_t)t * top + r) * D + d], acc);
+  for (int r = 0; r < top; ++r) {
+    const size_t u = (size_t)t * top + r;
+    acc = fmaf(wts[u], part[(slot ? (size_t)slot[u] : u) * D + d], acc);
+  }
   float* o = y + (size_t)t * ldy + d;
   *o = accumulate ? *o + acc : acc;
 }
@@ -423,6 +433,7 @@ extern "C" int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up
   HB_REQUIRE(n_tokens > 0 && D > 0 && E > 0 && F > 0 && top > 0, "moe_experts_grouped: sizes must be positive");
   HB_REQUIRE(E <= MG_MAX_EXPERTS, "moe_experts_grouped: at most %d experts", MG_MAX_EXPERTS);
   HB_REQUIRE(D % 8 == 0 && F % 8 == 0 && ld % 8 == 0, "moe_experts_grouped: widths must be multiples of 8");
+  HB_REQUIRE(gated == 0 || gated == 2, "moe_experts_grouped: gated experts need their gate and up rows in groups of 8");
   HB_REQUIRE(n_tokens <= 65535, "moe_experts_grouped: at most 65535 tokens per call");
   const int n_pairs = n_tokens * top;
   int* pair_off = scratch;
@@ -436,7 +447,95 @@ extern "C" int hb_moe_experts_grouped_bf16(const void* h, int ld, const void* up
             mid, F, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, n_up, D, top, act, gated);
   hb_launch(moe_grouped_gemm_kernel<false>, dim3(max_tiles, ceil_div(D, MG_TN)), dim3(MG_THREADS), 0, s, (const bf16*)mid, F,
             (const bf16*)down, (void*)part, D, (const int*)pair_off, (const int*)tile_off, (const int*)list, E, D, F, top, act, 0);
-  hb_launch(moe_combine_kernel, dim3(ceil_div(D, 256), n_tokens), dim3(256), 0, s, (const float*)part, weights, y, ldy, D, top, accumulate);
+  hb_launch(moe_combine_kernel, dim3(ceil_div(D, 256), n_tokens), dim3(256), 0, s, (const float*)part, weights, y, ldy, D, top, accumulate, (const int*)nullptr);
   HB_CHECK_LAUNCH("moe_experts_grouped");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Long prompts, gated experts with silu, bfloat16: the grouped products on tcgen05.  The pairs are sorted by
+// expert into a buffer in which every expert's run is padded to whole tiles of 128 rows, so that a tile of the
+// tensor-memory product (gemm_tcgen05.cu, grouped mode) belongs to one expert:
+//   sort:     counts per expert, padded offsets, slot[pair] = its row, tile_expert[tile], rows in use
+//   gather:   sorted[slot[pair]] = h[pair / top]
+//   product:  mid = silu(gate) * up of sorted x W1_e (the dense feed-forward's fused epilogue)
+//   product:  part = mid x W2_e (float)
+//   combine:  y[t] (+)= sum_r weights[t, r] * part[slot[t * top + r]]
+// Rows of padding are computed and never read.  A pair's numbers do not depend on its place.
+__global__ void __launch_bounds__(1024)
+moe_sort_padded_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict__ slot, int* __restrict__ tile_expert,
+                       int* __restrict__ rows_used, int max_tiles) {
+  __shared__ int cnt[MG_MAX_EXPERTS], off[MG_MAX_EXPERTS];
+  pdl_wait();
+  pdl_launch();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int u = threadIdx.x; u < n_pairs; u += blockDim.x) atomicAdd(&cnt[ids[u]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tl = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = tl * 128;
+      const int n = (cnt[e] + 127) / 128;
+      for (int i = 0; i < n && tl + i < max_tiles; ++i) tile_expert[tl + i] = e;
+      tl += n;
+    }
+    *rows_used = (tl < max_tiles ? tl : max_tiles) * 128;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int u = threadIdx.x; u < n_pairs; u += blockDim.x) {
+    const int e = ids[u];
+    slot[u] = off[e] + atomicAdd(&cnt[e], 1);
+  }
+}
+
+__global__ void moe_gather_rows_kernel(const bf16* __restrict__ h, int ld, const int* __restrict__ slot, bf16* __restrict__ sorted,
+                                       int D8, int top) {
+  pdl_wait();
+  pdl_launch();
+  const int u = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(h + (size_t)(u / top) * ld);
+  uint4* dst = reinterpret_cast<uint4*>(sorted + (size_t)slot[u] * D8 * 8);
+  for (int i = threadIdx.x; i < D8; i += blockDim.x) dst[i] = src[i];
+}
+
+// Rows of the sorted, padded buffers for n_tokens * top pairs of E experts.
+extern "C" int hb_moe_experts_tc_rows(int n_tokens, int E, int top) {
+  const long long tiles = ((long long)n_tokens * top + 127) / 128 + E;
+  return tiles * 128 > 2147483647LL ? -1 : (int)(tiles * 128);
+}
+
+// up [E, 2F, D] with gate and up rows in groups of 8; ints: n_tokens * top + rows / 128 + 1; sorted [rows, D] and
+// mid [rows, F] bfloat16, part [rows, D] floats, with rows = hb_moe_experts_tc_rows(...).
+extern "C" int hb_moe_experts_tc_bf16(const void* h, int ld, const void* up, const void* down, const int* ids,
+                                      const float* weights, int* ints, void* sorted, void* mid, float* part, float* y, int ldy,
+                                      int n_tokens, int D, int E, int F, int top, int accumulate, int* error_flag,
+                                      void* stream) {
+  HB_REQUIRE(n_tokens > 0 && D > 0 && E > 0 && F > 0 && top > 0, "moe_experts_tc: sizes must be positive");
+  HB_REQUIRE(E <= MG_MAX_EXPERTS, "moe_experts_tc: at most %d experts", MG_MAX_EXPERTS);
+  HB_REQUIRE(D % 8 == 0 && F % 8 == 0 && ld % 8 == 0 && ((uintptr_t)h & 15) == 0, "moe_experts_tc: widths must be multiples of 8, rows 16-byte aligned");
+  HB_REQUIRE(n_tokens <= 65535, "moe_experts_tc: at most 65535 tokens per call");
+  const int rows = hb_moe_experts_tc_rows(n_tokens, E, top);
+  HB_REQUIRE(rows > 0, "moe_experts_tc: too many pairs");
+  const int n_pairs = n_tokens * top, max_tiles = rows / 128;
+  int* slot = ints;
+  int* tile_expert = ints + n_pairs;
+  int* rows_used = tile_expert + max_tiles;
+  cudaStream_t s = (cudaStream_t)stream;
+  hb_launch(moe_sort_padded_kernel, dim3(1), dim3(1024), 0, s, ids, n_pairs, E, slot, tile_expert, rows_used, max_tiles);
+  hb_launch(moe_gather_rows_kernel, dim3(n_pairs), dim3(D / 8 >= 128 ? 128 : 64), 0, s, (const bf16*)h, ld, (const int*)slot,
+            (bf16*)sorted, D / 8, top);
+  HB_CHECK_LAUNCH("moe_experts_tc (sort, gather)");
+  int rc = hb_gemm_tcgen05_grouped_bf16(sorted, D, up, D, mid, F, rows, 2 * F, D, E, HB_EPI_SWIGLU, rows_used, tile_expert,
+                                        error_flag, stream);
+  if (rc) return rc;
+  rc = hb_gemm_tcgen05_grouped_bf16(mid, F, down, F, part, D, rows, D, F, E, HB_EPI_STORE_F32, rows_used, tile_expert,
+                                    error_flag, stream);
+  if (rc) return rc;
+  hb_launch(moe_combine_kernel, dim3(ceil_div(D, 256), n_tokens), dim3(256), 0, s, (const float*)part, weights, y, ldy, D, top,
+            accumulate, (const int*)slot);
+  HB_CHECK_LAUNCH("moe_experts_tc (combine)");
   return 0;
 }

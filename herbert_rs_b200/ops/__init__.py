@@ -83,6 +83,9 @@ _SIGS = {
                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_moe_experts_grouped_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_moe_experts_tc_rows": [c_int, c_int, c_int],
+    "hb_moe_experts_tc_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "hb_latent_attention_mma_ok": [c_int, c_int],
     "hb_latent_attention_mma_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
@@ -115,7 +118,7 @@ def _fn(name: str):
 
 # kernels each launcher starts (for honest launch counts)
 _KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2, "hb_argmax": 2, "hb_sample": 2, "hb_moe_experts": 2,
-                     "hb_moe_experts_grouped_bf16": 4}
+                     "hb_moe_experts_grouped_bf16": 4, "hb_moe_experts_tc_bf16": 5}
 _launches = 0
 
 
@@ -470,15 +473,49 @@ def moe_route(h, w_router, ids, weights, top, renorm=False, score=0, groups=1, k
 MOE_GROUPED_MIN_TOKENS = 32
 
 
-def moe_grouped_ok(h, up) -> bool:
+MOE_TC_MIN_PAIRS = 512
+GATED_HALVES, GATED_GROUPS_OF_8 = 1, 2     # layouts of a gated expert's first matrix (see `moe_experts`)
+
+
+def moe_grouped_ok(h, up, gated=0) -> bool:
     """Whether a step's routed feed-forward goes through the grouped tensor-core product: bfloat16, enough
     tokens that an expert's matrices are worth reading once per tile of pairs, widths in 16-byte pieces."""
     E, F, D = up.shape
+    if gated:
+        F //= 2
     return (options.moe_grouped and h.dtype == torch.bfloat16 and MOE_GROUPED_MIN_TOKENS <= h.shape[0] <= 65535
-            and D % 8 == 0 and F % 8 == 0 and h.stride(0) % 8 == 0 and E <= 1024 and h.data_ptr() % 16 == 0)
+            and D % 8 == 0 and F % 8 == 0 and h.stride(0) % 8 == 0 and E <= 1024 and h.data_ptr() % 16 == 0
+            and gated in (0, GATED_GROUPS_OF_8))
 
 
-def moe_experts_grouped(h, up, down, ids, weights, y, act, accumulate, scratch, gated=False) -> None:
+def moe_tc_ok(h, up, top, gated, act) -> bool:
+    """Whether the grouped products run on tcgen05: what `moe_grouped_ok` asks, gated experts with silu (the
+    product's fused epilogue), and enough (token, expert) pairs that tiles of 128 rows per expert fill."""
+    return (options.moe_tc and moe_grouped_ok(h, up, gated) and gated == GATED_GROUPS_OF_8 and act == ACT_SILU
+            and h.shape[0] * int(top) >= MOE_TC_MIN_PAIRS)
+
+
+def moe_experts_tc(h, up, down, ids, weights, y, accumulate, scratch) -> None:
+    """moe_experts for long prompts, gated experts with silu: the pairs sorted by expert into runs padded to tiles of
+    128 rows, both products on tcgen05 (the first with the gated activation in its epilogue)."""
+    _check(h, torch.bfloat16, "h"); _check(up, torch.bfloat16, "up"); _check(down, torch.bfloat16, "down"); _check(y, torch.float32, "y")
+    T, top = ids.shape
+    E, F2, D = up.shape
+    F = F2 // 2
+    rows = int(_fn("hb_moe_experts_tc_rows")(T, E, top))
+    if rows <= 0:
+        raise BackendError("moe_experts_tc: too many (token, expert) pairs")
+    ints = scratch((T * top + rows // 128 + 1,), torch.int32)
+    srt = scratch((rows, D), torch.bfloat16)
+    mid = scratch((rows, F), torch.bfloat16)
+    part = scratch((rows, D), torch.float32)
+    _tcgen05_workspace(y.device)
+    _run("hb_moe_experts_tc_bf16", h.data_ptr(), h.stride(0), up.data_ptr(), down.data_ptr(), ids.data_ptr(), weights.data_ptr(),
+         ints.data_ptr(), srt.data_ptr(), mid.data_ptr(), part.data_ptr(), y.data_ptr(), y.stride(0), T, D, E, F, top,
+         1 if accumulate else 0, _error_flag(y.device).data_ptr(), _stream())
+
+
+def moe_experts_grouped(h, up, down, ids, weights, y, act, accumulate, scratch, gated=0) -> None:
     """moe_experts for many tokens: pairs grouped by expert on the device, tiles of 64 pairs on the tensor cores."""
     _check(h, torch.bfloat16, "h"); _check(up, torch.bfloat16, "up"); _check(down, torch.bfloat16, "down"); _check(y, torch.float32, "y")
     T, top = ids.shape
@@ -490,19 +527,20 @@ def moe_experts_grouped(h, up, down, ids, weights, y, act, accumulate, scratch, 
     part = scratch((T * top, D), torch.float32)
     _run("hb_moe_experts_grouped_bf16", h.data_ptr(), h.stride(0), up.data_ptr(), down.data_ptr(), ids.data_ptr(), weights.data_ptr(),
          ints.data_ptr(), mid.data_ptr(), part.data_ptr(), y.data_ptr(), y.stride(0), T, D, E, F, top, int(act),
-         1 if gated else 0, 1 if accumulate else 0, _stream())
+         int(gated), 1 if accumulate else 0, _stream())
 
 
-def moe_experts(h, up, down, ids, weights, mid, y, act, accumulate=False, gated=False) -> None:
+def moe_experts(h, up, down, ids, weights, mid, y, act, accumulate=False, gated=0) -> None:
     """y[t] (+)= sum_r weights[t, r] * down[e] act(up[e] h[t]), e = ids[t, r]; up [E, F, D], down [E, D, F] in
-    h's dtype; mid [T * top, F] scratch in h's dtype; y float.  gated: up is [E, 2F, D] with gate and up rows in
-    turn and an expert is down[e] (act(gate h) * (up h))."""
+    h's dtype; mid [T * top, F] scratch in h's dtype; y float.  gated: up is [E, 2F, D] and an expert is
+    down[e] (act(gate h) * (up h)), with the gate and up rows in turn in groups of 8 (GATED_GROUPS_OF_8) or all
+    gate rows before all up rows (GATED_HALVES)."""
     _check(h, None, "h"); _check(up, h.dtype, "up"); _check(down, h.dtype, "down"); _check(mid, h.dtype, "mid"); _check(y, torch.float32, "y")
     if not (up.is_contiguous() and down.is_contiguous() and mid.is_contiguous()):
         raise BackendError("moe_experts: up, down and mid must be contiguous")
     _run("hb_moe_experts", dtype_code(h.dtype), h.data_ptr(), h.stride(0), up.data_ptr(), down.data_ptr(), ids.data_ptr(),
          weights.data_ptr(), mid.data_ptr(), y.data_ptr(), y.stride(0), h.shape[0], h.shape[1], down.shape[2], ids.shape[1],
-         int(act), 1 if gated else 0, 1 if accumulate else 0, _stream())
+         int(act), int(gated), 1 if accumulate else 0, _stream())
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:

@@ -41,5 +41,7 @@ class KernelOptions:
     latent_max_splits: int = 16
     # Routed feed-forward, bfloat16, steps of 32 tokens and more: pairs grouped by expert, tiles on the tensor cores.
     moe_grouped: bool = True
+    # ... and, for gated experts with silu and 512 (token, expert) pairs or more, those tiles on tcgen05.
+    moe_tc: bool = True
     # Steps of 512 rows and more, heads of 128: per-head norm, rotation and cache write in the q/k/v product's epilogue.
     qkv_epilogue: bool = True

@@ -8,8 +8,9 @@ expert by its index; which experts a token uses never reaches the host, so a rec
 
 Options of the spec: sigmoid scores; groups of experts of which only the best stay open to the choice;
 a factor on the weights; gated experts, out_e = Down_e (act(Gate_e h) * (Up_e h)), whose gate and up
-rows are stored in turn in one [E, 2F, D] stack (row 2f: gate f, row 2f + 1: up f); a shared dense
-feed-forward that every token passes and that is added to the experts' sum.
+rows are stored in one [E, 2F, D] stack, in turn in groups of 8 (the dense gated feed-forward's layout,
+which the tensor-core products' epilogues read) or, where F is no multiple of 8, all gate rows first; a
+shared dense feed-forward that every token passes and that is added to the experts' sum.
 """
 
 from __future__ import annotations
@@ -20,6 +21,7 @@ from .. import ops
 from ..errors import ConfigError
 from ..registry import build_part, register_part
 from .base import FeedForward, ParamSpec
+from .swiglu import join_gate_up
 
 SCORES = {"softmax": 0, "sigmoid": 1}
 
@@ -63,10 +65,11 @@ class RoutedFeedForward(FeedForward):
     def load(self, t):
         s = self.spec
         self.router = t[s.router_name].contiguous()
+        self.gated = 0
         if s.gated:
-            # [E, F, 2, D] -> [E, 2F, D]: gate and up rows in turn
-            self.up = torch.stack([torch.stack([t[self._names(e)[0]], t[self._names(e)[1]]], dim=1)
-                                   for e in range(s.num_experts)]).reshape(s.num_experts, 2 * s.expert_size, s.hidden_size).contiguous()
+            joined = [join_gate_up(t[self._names(e)[0]], t[self._names(e)[1]]) for e in range(s.num_experts)]
+            self.up = torch.stack([j[0] for j in joined]).contiguous()
+            self.gated = ops.GATED_GROUPS_OF_8 if joined[0][1] else ops.GATED_HALVES
         else:
             self.up = torch.stack([t[self._names(e)[0]] for e in range(s.num_experts)]).contiguous()
         self.down = torch.stack([t[self._names(e)[-1]] for e in range(s.num_experts)]).contiguous()
@@ -86,11 +89,13 @@ class RoutedFeedForward(FeedForward):
         weights = ws.take((T, s.top_k), torch.float32)
         ops.moe_route(h, self.router, ids, weights, s.top_k, s.renormalize, SCORES[s.score], s.groups, s.keep_groups,
                       s.group_top, s.weight_scale)
-        if ops.moe_grouped_ok(h, self.up):
-            ops.moe_experts_grouped(h, self.up, self.down, ids, weights, residual, self.act, accumulate, ws.take, gated=s.gated)
+        if ops.moe_tc_ok(h, self.up, s.top_k, self.gated, self.act):
+            ops.moe_experts_tc(h, self.up, self.down, ids, weights, residual, accumulate, ws.take)
+        elif ops.moe_grouped_ok(h, self.up, self.gated):
+            ops.moe_experts_grouped(h, self.up, self.down, ids, weights, residual, self.act, accumulate, ws.take, gated=self.gated)
         else:
             mid = ws.take((T * s.top_k, s.expert_size), h.dtype)
-            ops.moe_experts(h, self.up, self.down, ids, weights, mid, residual, self.act, accumulate, gated=s.gated)
+            ops.moe_experts(h, self.up, self.down, ids, weights, mid, residual, self.act, accumulate, gated=self.gated)
         if self.shared is not None:
             self.shared.forward(h, residual, batch, accumulate=True)
 

@@ -137,19 +137,29 @@ def test_router_with_groups_and_gated_experts(dtype, experts, top, groups, keep)
         for j in range(top):
             e = int(ids[t, j])
             ref[t] += float(wts[t, j]) * P.gated_expert(h[t:t + 1].double(), W[f"e{e}.gate"], W[f"e{e}.up"], W[f"e{e}.down"])[0]
-    stacked = torch.stack([gate, up], dim=2).reshape(experts, 2 * F, D).contiguous().to(DEV)
+    # gate and up rows in turn in groups of 8, and all gate rows before all up rows
+    stacked = torch.cat([gate.view(experts, F // 8, 8, D), up.view(experts, F // 8, 8, D)], dim=2).reshape(experts, 2 * F, D).contiguous().to(DEV)
+    halves = torch.cat([gate, up], dim=1).contiguous().to(DEV)
     mid = torch.zeros(T * top, F, dtype=td, device=DEV)
     y = torch.full((T, D), 5.0, device=DEV)
-    ops.moe_experts(h.to(DEV), stacked, down.to(DEV), ids, wts, mid, y, ops.ACT_SILU, gated=True)
+    ops.moe_experts(h.to(DEV), stacked, down.to(DEV), ids, wts, mid, y, ops.ACT_SILU, gated=ops.GATED_GROUPS_OF_8)
     assert_close(to_np(y), ref.numpy(), dtype, "a warp per output")
-    ops.moe_experts(h.to(DEV), stacked, down.to(DEV), ids, wts, mid, y, ops.ACT_SILU, accumulate=True, gated=True)
-    assert_close(to_np(y), 2 * ref.numpy(), dtype, "added")
+    ops.moe_experts(h.to(DEV), halves, down.to(DEV), ids, wts, mid, y, ops.ACT_SILU, accumulate=True, gated=ops.GATED_HALVES)
+    assert_close(to_np(y), 2 * ref.numpy(), dtype, "added, the other layout")
     if dtype == "bfloat16":
-        assert ops.moe_grouped_ok(h.to(DEV), stacked)
+        take = lambda shape, dt: torch.empty(shape, dtype=dt, device=DEV)       # noqa: E731
+        assert ops.moe_grouped_ok(h.to(DEV), stacked, ops.GATED_GROUPS_OF_8) and not ops.moe_grouped_ok(h.to(DEV), halves, ops.GATED_HALVES)
         y2 = torch.full((T, D), 5.0, device=DEV)
-        ops.moe_experts_grouped(h.to(DEV), stacked, down.to(DEV), ids, wts, y2, ops.ACT_SILU, False,
-                                lambda shape, dt: torch.empty(shape, dtype=dt, device=DEV), gated=True)
+        ops.moe_experts_grouped(h.to(DEV), stacked, down.to(DEV), ids, wts, y2, ops.ACT_SILU, False, take, gated=ops.GATED_GROUPS_OF_8)
         assert_close(to_np(y2), ref.numpy(), dtype, "grouped by expert")
+        assert not ops.moe_tc_ok(h.to(DEV), stacked, top, ops.GATED_GROUPS_OF_8, ops.ACT_SILU) or T * top >= 512
+        y3 = torch.full((T, D), 5.0, device=DEV)
+        ops.moe_experts_tc(h.to(DEV), stacked, down.to(DEV), ids, wts, y3, False, take)
+        torch.cuda.synchronize()
+        ops.check_kernel_errors()
+        assert_close(to_np(y3), ref.numpy(), dtype, "grouped by expert, tcgen05")
+        ops.moe_experts_tc(h.to(DEV), stacked, down.to(DEV), ids, wts, y3, True, take)
+        assert_close(to_np(y3), 2 * ref.numpy(), dtype, "grouped by expert, tcgen05, added")
 
 
 class _Cache:
