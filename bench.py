@@ -271,7 +271,7 @@ def _launcher_work(name, n, ctx):
             return n * 6.0 * T * D, n * T * D * (4 + 4 + 4 + es)
         if name == "hb_qk_prepare_cache":
             return n * 2.0 * T * (H + KV) * hd, n * T * (H + KV) * hd * (4 + es)
-        if name in ("hb_moe_experts", "hb_moe_experts_grouped_bf16"):
+        if name in ("hb_moe_experts", "hb_moe_experts_grouped_bf16", "hb_moe_experts_tc_bf16"):
             E, top, F = ctx["experts"], ctx["top"], ctx["expert_ff"]
             return n * 6.0 * T * top * F * D, n * (min(E, T * top) * 3 * F * D * es + T * D * (es + 4))
         if name == "hb_moe_route":
