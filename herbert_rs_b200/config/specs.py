@@ -156,7 +156,7 @@ class RoutedFFSpec:
     `group_top`: the experts form `groups` equal groups of neighbours, a group's score is the sum of its
     `group_top` largest scores, and only experts of the `keep_groups` best groups can be chosen;
     `weight_scale`: a factor on every chosen weight; `shared`: a dense gated feed-forward (its own
-    spec, tensors under `shared_prefix`) that runs for every token and is added."""
+    spec, which also names its tensors) that runs for every token and is added."""
 
     hidden_size: int
     num_experts: int

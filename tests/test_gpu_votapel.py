@@ -34,7 +34,7 @@ def mixed(tmp_path_factory):
     layers = [(U.attention(heads=4, kv_heads=2, dim=16), U.moe()),
               (U.attention(heads=2, kv_heads=1, dim=64, every=3, coef=0.7), None),
               (U.attention(heads=3, kv_heads=3, dim=24, softcap=None, coef=None), U.moe()),
-              (U.attention(heads=2, kv_heads=2, dim=128, softcap=3.0, every=64), U.moe())]
+              (U.attention(heads=2, kv_heads=2, dim=128, softcap=3.0, every=50), U.moe())]
     return U.make(tmp_path_factory.mktemp("votapel_mixed"), layers, seed=3)
 
 
@@ -367,7 +367,7 @@ def test_a_temperature_period_one_off_shows(tmp_path):
 OTHER = {
     "one_head_top_one": ([(U.attention(heads=1, kv_heads=1, dim=8, every=1), U.moe(experts=2, top=1, groups=2, keep=1, ff=8, shared=8, scale=1.0)),
                           (U.attention(heads=1, kv_heads=1, dim=8, coef=None), None)], dict(vocab=77, width=40, mult=1.0, eps=1e-6)),
-    "wide_heads": ([(U.attention(heads=6, kv_heads=2, dim=96, every=64), U.moe(experts=9, top=6, groups=3, keep=2, ff=40, shared=None)),
+    "wide_heads": ([(U.attention(heads=6, kv_heads=2, dim=96, every=40), U.moe(experts=9, top=6, groups=3, keep=2, ff=40, shared=None)),
                     (U.attention(heads=5, kv_heads=5, dim=48, softcap=50.0), U.moe(experts=9, top=6, groups=3, keep=2, ff=72, shared=136))],
                    dict(vocab=300, width=136, mult=0.3)),
     "odd_sizes": ([(U.attention(heads=3, kv_heads=1, dim=10, every=4), U.moe(experts=3, top=3, groups=1, keep=1, ff=12, shared=30)),
