@@ -11,6 +11,8 @@
 //   online softmax in float (running m, l per head),  O += P V  (V through ldmatrix.trans).
 // Warps, then splits, are merged with the usual rescaling; every split writes (m, l, O) to
 // scratch memory and a second kernel combines them:  out = sum_s e^{m_s - m} O_s / sum_s e^{m_s - m} l_s.
+// When the value plane is the key plane itself (a mixer whose values are its keys) a tile is fetched once and the
+// second product reads it where the first did.
 // Keys visible to the query at position p: lo..p, lo = max(0, p - window + 1) if window > 0.
 #include <stdlib.h>
 
@@ -118,6 +120,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
     }
   }
   const unsigned smem_u = (unsigned)__cvta_generic_to_shared(smem);
+  const bool same_plane = a.kcache == a.vcache;
   auto issue = [&](int tile, int stage) {
     const int page = page_ids[tile - first_tile];
     const size_t off = ((size_t)page * a.nkv + kvh) * head_elems + (size_t)(tile % tiles_per_page) * AD_TILE * hd;
@@ -129,7 +132,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
     for (int i = 0; i < SLOTS; ++i) {
       if (s_off[i] >= 0) {
         cp_async16_s(ks + s_off[i], kg + g_off[i]);
-        cp_async16_s(vs + s_off[i], vg + g_off[i]);
+        if (!same_plane) cp_async16_s(vs + s_off[i], vg + g_off[i]);      // values that are the keys: one copy serves both
       }
     }
   };
@@ -177,7 +180,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
     if (S == 2) cp_async_wait<1>(); else if (S == 3) cp_async_wait<2>(); else cp_async_wait<3>();
     __syncthreads();
     const unsigned ks = smem_u + (unsigned)(it % S) * 2 * tile_bytes;
-    const unsigned vs = ks + tile_bytes;
+    const unsigned vs = same_plane ? ks : ks + tile_bytes;
     const int key0 = tile * AD_TILE + warp * 16;
     if (key0 <= p && key0 + 15 >= lo) {
       // ---- S = Q K^T for this warp's 16 keys -------------------------------------------------
@@ -358,6 +361,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
     s_off[i] = r * row_bytes + cc * 16;
   }
   const unsigned smem_u = (unsigned)__cvta_generic_to_shared(smem);
+  const bool same_plane = a.kcache == a.vcache;
   auto issue = [&](int tile, int stage) {
     const int page = page_ids[tile - t0];
     const size_t off = ((size_t)page * a.nkv + kvh) * head_elems + (size_t)(tile % tiles_per_page) * AD_TILE * HD;
@@ -368,7 +372,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
 #pragma unroll
     for (int i = 0; i < SLOTS; ++i) {
       cp_async16_s(ks + s_off[i], kg + g_off[i]);
-      cp_async16_s(vs + s_off[i], vg + g_off[i]);
+      if (!same_plane) cp_async16_s(vs + s_off[i], vg + g_off[i]);
     }
   };
   const int S = a.stages;
@@ -457,7 +461,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
     if (S == 2) cp_async_wait<1>(); else if (S == 3) cp_async_wait<2>(); else cp_async_wait<3>();
     __syncthreads();
     const unsigned ks = smem_u + (unsigned)(it % S) * 2 * tile_bytes;
-    const unsigned vs = ks + tile_bytes;
+    const unsigned vs = same_plane ? ks : ks + tile_bytes;
     const int key0 = tile * AD_TILE + warp * 16;
     if (key0 <= p && key0 + 15 >= lo) {
       // ---- S^T = K Q^T: rows = this warp's 16 keys, columns = heads ------------------------------

@@ -80,6 +80,7 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillAr
   // This thread's first 16-byte chunk of a tile and the step to its next one (no division in the loop).
   const int chunk_r0 = threadIdx.x / chunks_per_row, chunk_c0 = threadIdx.x % chunks_per_row;
   const int step_r = AP_THREADS / chunks_per_row, step_c = AP_THREADS % chunks_per_row;
+  const bool same_plane = a.kcache == a.vcache;      // values that are the keys: a tile is fetched once and read twice
   auto issue = [&](int tile, int stage) {
     const int page = page_ids[tile - first_tile];
     const size_t off = ((size_t)page * a.nkv + kvh) * head_elems + (size_t)(tile % tiles_per_page) * AP_TILE * hd;
@@ -90,7 +91,7 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillAr
     int r = chunk_r0, cc = chunk_c0;
     while (r < AP_TILE) {
       cp_async16(ks + r * row_bytes + cc * 16, kg + (size_t)r * hd + cc * 8);
-      cp_async16(vs + r * row_bytes + cc * 16, vg + (size_t)r * hd + cc * 8);
+      if (!same_plane) cp_async16(vs + r * row_bytes + cc * 16, vg + (size_t)r * hd + cc * 8);
       r += step_r;
       cc += step_c;
       if (cc >= chunks_per_row) {
@@ -153,7 +154,7 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillAr
     if (S == 2) cp_async_wait<1>(); else cp_async_wait<2>();
     __syncthreads();
     const unsigned char* ks = smem + (size_t)(it % S) * 2 * tile_bytes;
-    const unsigned char* vs = ks + tile_bytes;
+    const unsigned char* vs = same_plane ? ks : ks + tile_bytes;
     const int key0 = tile * AP_TILE;
     if (warp_active && key0 <= wp_last && key0 + AP_TILE - 1 >= wlo) {
       // ---- S = Q K^T : 16 queries x 64 keys ---------------------------------------------------------
