@@ -21,6 +21,9 @@
 //              rescaled, only when the tile's maximum exceeds it by more than 2^8 (a factor that
 //              cancels in O / l), which after the first tiles almost never happens, so O is not
 //              touched between products.
+// Options: a cap on the scores (s <- cap * tanh(s * scale / cap), applied by the row thread before the mask; such
+// scores are then final, times log2 e, and the exponential's multiply-add takes a factor 1), and a sink per
+// query head (the row starts at m = sink, l = 1: a first key without a value).
 // A head pair whose second head does not exist (an odd number of query heads per key/value head)
 // runs the first head alone.  CTAs are persistent and take items from a counter, longest first.
 // Every wait on an mbarrier is bounded; a wait that runs out sets *error_flag and the CTA winds down.
@@ -47,7 +50,6 @@ struct PrefillTcArgs {
   int* error_flag;
   int n_seqs, q_tiles;   // items = q_tiles x n_seqs x nkv x head pairs (some without queries when the sequences differ in length)
   int* work_counter;     // next item; zero when the kernel starts, and left at zero by the CTA that fetches last
-  float scale;           // the scale itself, for the capped form
   float softcap;         // > 0: score <- softcap * tanh(score * scale / softcap)
   const float* sink;     // [nh] or null: e^{sink} joins the row's sum (the row starts at m = sink, l = 1)
 };
@@ -491,7 +493,7 @@ extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens
   if (rc) return rc;
   const int q_tiles = ceil_div(max_q_len, PT_Q);
   PrefillTcArgs a{(bf16*)out, ldo, seq_start, seq_pos0, seq_pages, pages_stride, nh, nkv, page_size,
-                  scale * 1.4426950408889634f, window, error_flag, n_seqs, q_tiles, work_counter, scale, softcap, sink};
+                  scale * 1.4426950408889634f, window, error_flag, n_seqs, q_tiles, work_counter, softcap, sink};
   cudaStream_t s = (cudaStream_t)stream;
   const int pairs = (nh / nkv + 1) / 2;
   const long long items = (long long)q_tiles * n_seqs * nkv * pairs;
