@@ -352,6 +352,31 @@ def test_sharp_attention_over_small_pages_and_long_decoding(tmp_path, dtype):
     eng.cache.check()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_long_prompt_and_its_continuation(tmp_path, dtype):
+    """600 tokens at once (several tiles of pairs per expert, ten pages of keys, the temperature far along), then the
+    same prompt in two portions and 24 tokens decoded one by one."""
+    layers = [(U.attention(heads=4, kv_heads=2, dim=32, every=100, softcap=15.0), U.moe(experts=8, top=2, groups=4, keep=2, ff=48, shared=72)),
+              (U.attention(heads=2, kv_heads=1, dim=64, every=100, coef=0.2), U.moe(experts=8, top=2, groups=4, keep=2, ff=48, shared=72))]
+    d, pm = U.make(tmp_path / "long", layers, seed=13, width=128, vocab=500, max_positions=1024)
+    ids = ids_for(np.random.default_rng(13), 500, 624)
+    rows = [0, 1, 63, 64, 99, 100, 299, 300, 511, 512, 598, 599] + list(range(600, 624))
+    arith = torch.float32 if dtype == "bfloat16" else torch.float64
+    ref = pm.logits(ids).numpy()[rows]
+    eng = engine_for(d, dtype, max_tokens=2048)
+    for cuts in ([600], [333, 267]):
+        s, got, at = eng.alloc_slot(), [], 0
+        for n in cuts + [1] * 24:
+            want = [r - at for r in rows if at <= r < at + n]
+            out = eng.step([(s, ids[at:at + n])], [want])
+            if want:
+                got.append(to_np(out))
+            at += n
+        eng.free_slot(s)
+        assert_close(np.concatenate(got), ref, dtype, f"prompt in {len(cuts)}", plain=pm, ids=ids, rows=rows, arith=arith)
+    eng.check_kernels()
+
+
 def test_a_temperature_period_one_off_shows(tmp_path):
     """The comparison is sharp enough to see a period that is one position too long or too short."""
     d, pm = U.make(tmp_path / "t", [(U.attention(every=9, coef=0.8, sharp=2.0), None)], seed=1)
