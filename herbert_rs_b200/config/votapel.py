@@ -28,6 +28,7 @@ from ..errors import ConfigError
 from .base import Reader
 from .specs import AttentionSpec, BlockSpec, ModelSpec, NormSpec, RoutedFFSpec, SwiGLUSpec, identity_schedule
 
+NO_POSITION_LIMIT = 1 << 30
 NORM_OFFSET = 1.0       # stored norm weights lie around zero: the factor is 1 + w
 GROUP_TOP = 2           # a group's score: the sum of its two largest scores
 
@@ -58,7 +59,8 @@ class VotapelConfig:
         r = Reader(c)
         vocab = r.integer("vocab", minimum=1)
         width = r.integer("width", minimum=1)
-        max_positions = r.integer("max_positions", minimum=1)
+        # the position table's length; a configuration without the key leaves it to the stored tensor's shape
+        max_positions = r.integer("max_positions", NO_POSITION_LIMIT, minimum=1)
         eps = _sub(r, "norm").number("eps")
         if not eps > 0.0:
             raise ConfigError("norm.eps must be > 0")

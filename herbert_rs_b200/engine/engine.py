@@ -39,7 +39,8 @@ class Engine:
         ps = self.rt.page_size
         num_pages = max(1, -(-int(max_tokens) // ps))
         num_slots = max_slots if max_slots is not None else min(num_pages, 1024)
-        limit = model.spec.max_position if max_seq_len is None else min(max_seq_len, model.spec.max_position)
+        longest = model.longest_sequence() if hasattr(model, "longest_sequence") else model.spec.max_position
+        limit = longest if max_seq_len is None else min(max_seq_len, longest)
         self.cache = SequenceCache(model.cache_needs(), model.reads_cache_of(), num_pages, num_slots,
                                    page_size=ps, max_seq_len=limit, dtype=self.rt.dtype, device=self.rt.device)
         self._host = torch.empty(1 << 14, dtype=torch.int32).pin_memory()

@@ -24,6 +24,10 @@ from ..parts.base import ParamSpec
 from ..registry import build_part
 
 
+# A spec whose positions have no bound of their own says so with this number (or more).
+NO_POSITION_LIMIT = 1 << 30
+
+
 class DecoderModel:
     def __init__(self, spec: ModelSpec, rt):
         self.spec, self.rt = spec, rt
@@ -44,7 +48,9 @@ class DecoderModel:
         s = self.spec
         out = {s.embed_name: ParamSpec((s.vocab_size, s.hidden_size))}
         if s.position_table_name:
-            out[s.position_table_name] = ParamSpec((s.max_position, s.hidden_size))
+            # a configuration that does not say how many positions the table has leaves it to the stored tensor
+            rows = s.max_position if s.max_position < NO_POSITION_LIMIT else -1
+            out[s.position_table_name] = ParamSpec((rows, s.hidden_size), free_size=4096)
         for i, b in enumerate(self.blocks):
             for name, ps in b.param_specs().items():
                 out[self.block_prefix(i) + name] = ps
@@ -69,6 +75,11 @@ class DecoderModel:
 
     def load_position_table(self, t: torch.Tensor) -> None:
         self.position_table = t.contiguous()
+
+    def longest_sequence(self) -> int:
+        """The longest sequence the model can place: the spec's limit, and the position table's rows."""
+        n = self.spec.max_position
+        return n if self.position_table is None else min(n, int(self.position_table.shape[0]))
 
     def load_head(self, t: torch.Tensor) -> None:
         self.head = t.contiguous()

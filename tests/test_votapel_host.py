@@ -34,7 +34,7 @@ def test_configuration_is_read_from_the_nested_keys():
 
 
 @pytest.mark.parametrize("edit,message", [
-    (lambda c: c.pop("max_positions"), "max_positions"),
+    (lambda c: c.update(max_positions=0), "max_positions"),
     (lambda c: c["layers"][0].update(type="conv"), "unknown layer type"),
     (lambda c: c["layers"][0]["mixer"].update(vdim=8), "vdim"),
     (lambda c: c["layers"][0]["mixer"].update(kv_heads=3), "multiple of kv_heads"),
@@ -66,6 +66,17 @@ def test_declared_tensors_and_cache_need(tmp_path):
     assert model.graph_safe
     U.write(cfg, U.weights(cfg), tmp_path)
     assert P.PlainVotapel(str(tmp_path)).logits([1, 2, 3]).shape == (3, 131)
+
+
+def test_a_position_table_whose_length_only_the_tensor_gives(tmp_path):
+    cfg = U.config([(U.attention(), None)], max_positions=77)
+    t = U.weights(cfg)
+    del cfg["max_positions"]
+    model = build_model(cfg, hb.Runtime("cpu", torch.bfloat16))
+    assert model.param_specs()["pos"].shape == (-1, 64)
+    from herbert_rs_b200.weights.loader import fill_model
+    fill_model(model, lambda name: t[name], model.rt)
+    assert model.longest_sequence() == 77
 
 
 def test_a_missing_or_misshapen_tensor_is_reported(tmp_path):
